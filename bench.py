@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Benchmark of the AMO-BQ feature-cache hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one AMO-BQ G32 decode of the pre-quantised codes of a bf16 tensor
+[128, 446, 768] (43.8 M values) into a preallocated bf16 buffer -- the
+configuration the headline metric is quoted on.  Prints ONE JSON line.
+
+* ``value``     device-resident decode throughput in algorithmic GB/s
+                (1 + 3/G + 2 bytes per value, GB = 1e9), CUDA events over exactly
+                K launches on the launching stream; four input/output sets are
+                rotated so that every launch reads and writes memory that is not
+                in L2 (542 MB footprint vs 126 MB of L2).
+* ``roofline``  the same bytes / average launch time against the measured HBM
+                copy bandwidth in MEASURED_PEAKS.json.
+* ``e2e``       the same metric through the public reader API
+                (ZeroCopyTensorStreamer over a cache shard in host memory):
+                memory-mapped rows -> page-locked staging -> H2D -> decode, with a
+                device->host read of a per-batch completion word, every step.
+* ``cpu_baseline``  the C port of the reference's CPU decode (oracle/) on the host
+                cores of this box, on a bounded sample.
+* ``--impl reference``  times that CPU port alone, each step decoding a 16-sample
+                slice of the same workload, with all host threads.
+
+Multi-GPU (torchrun, one rank per GPU): shards are independent, every rank runs
+the same per-GPU work on its own data (weak scaling), no data-path collective.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPE = (128, 446, 768)
+G = 32
+METRIC = "amo_bq_g32_dequant_throughput"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(numel: int, g: int) -> float:
+    return numel * (1.0 + 3.0 / g + 2.0)
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def synthetic_codes(numel: int, g: int, seed: int, device):
+    """Random but well-formed codes: uniform uint8 codes and zero points, bf16 scales
+    spread log-uniformly over the range activations produce.  The decode kernel's
+    work does not depend on the values."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    ng = numel // g
+    q = torch.randint(0, 256, (numel,), dtype=torch.uint8, generator=gen)
+    zp = torch.randint(0, 256, (ng,), dtype=torch.uint8, generator=gen)
+    s = torch.exp(torch.rand(ng, generator=gen) * 6.0 - 7.0).to(torch.bfloat16)
+    return q.to(device), s.to(device), zp.to(device)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while a region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return
+        fd, self.path = tempfile.mkstemp(prefix="tcb_clocks_", suffix=".csv")
+        os.close(fd)
+        self.out = open(self.path, "w")
+        self.proc = subprocess.Popen([exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                      "-i", str(self.gpu_index)], stdout=self.out, stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except (ValueError, IndexError):
+            pass
+    return local_index
+
+
+# --------------------------------------------------------------------------- CPU
+
+def cpu_decode_rate(numel: int, g: int, budget_s: float, max_reps: int, nthreads: int):
+    """Best-of rate of the C port of the reference CPU decode; returns (GB/s, reps, seconds)."""
+    from oracle import amo_oracle as orc
+
+    rng = np.random.default_rng(0)
+    q = rng.integers(0, 256, numel, dtype=np.uint8)
+    zp = rng.integers(0, 256, numel // g, dtype=np.uint8)
+    s = torch.exp(torch.rand(numel // g) * 6.0 - 7.0).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    out = np.empty(numel, np.uint16)
+    orc.decompress(q, s, zp, g, nthreads=nthreads, out=out)  # warm-up, page-faults the output
+    best, reps, t_start = float("inf"), 0, time.perf_counter()
+    while reps < max_reps and time.perf_counter() - t_start < budget_s:
+        t0 = time.perf_counter()
+        orc.decompress(q, s, zp, g, nthreads=nthreads, out=out)
+        best = min(best, time.perf_counter() - t0)
+        reps += 1
+    return algorithmic_bytes(numel, g) / best / 1e9, reps, time.perf_counter() - t_start
+
+
+def run_reference_arm(args):
+    """CPU port of the reference decode, all host threads; step = one 16-sample slice."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import amo_oracle as orc
+
+    nthreads = orc.default_threads()
+    slice_shape = (16,) + SHAPE[1:]
+    numel = int(np.prod(slice_shape))
+    rng = np.random.default_rng(0)
+    n_sets = 8  # 8 x 16 samples = the full [128, 446, 768] workload, visited round-robin
+    sets = []
+    for _ in range(n_sets):
+        q = rng.integers(0, 256, numel, dtype=np.uint8)
+        zp = rng.integers(0, 256, numel // G, dtype=np.uint8)
+        s = torch.exp(torch.rand(numel // G) * 6.0 - 7.0).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+        sets.append((q, s, zp, np.empty(numel, np.uint16)))
+    for i in range(max(args.warmup, n_sets)):
+        q, s, zp, out = sets[i % n_sets]
+        orc.decompress(q, s, zp, G, nthreads=nthreads, out=out)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        q, s, zp, out = sets[i % n_sets]
+        orc.decompress(q, s, zp, G, nthreads=nthreads, out=out)
+    dt = time.perf_counter() - t0
+    value = algorithmic_bytes(numel, G) * args.steps / dt / 1e9
+    sample = f"each step decodes a [16,446,768] slice (1/8 of the workload, {numel} values) with {nthreads} threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8->bf16 (fp32 arithmetic)", "data": "synthetic",
+        "config": {"workload": "AMO-BQ G32 decode of [128,446,768] bf16 codes into a preallocated buffer",
+                   "group_size": G, "timing": "host wall clock, inputs in host memory"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# --------------------------------------------------------------------------- GPU
+
+def build_cache_shard(tc, directory: str, n_samples: int, seed: int, device) -> str:
+    """Writes one AMO-BQ G32 cache shard of [446, 768] samples with the GPU encoder."""
+    prefix = os.path.join(directory, "feat")
+    w = tc.FeatureCacheWriter(prefix, n_samples, SHAPE[1], SHAPE[2], group_size=G, amo_bq=True, amo_mode="balanced")
+    gen = torch.Generator(device=device).manual_seed(seed)
+    ch = torch.exp(0.5 * torch.randn(SHAPE[2], generator=gen, device=device))
+    done = 0
+    while done < n_samples:
+        b = min(64, n_samples - done)
+        x = torch.randn((b,) + SHAPE[1:], generator=gen, device=device) * ch
+        mask = torch.rand(x.shape, generator=gen, device=device) < 0.001
+        w.append(torch.where(mask, 20 * x, x).to(torch.bfloat16))
+        done += b
+    w.close()
+    return prefix
+
+
+def scratch_dir() -> str:
+    for base in ("/dev/shm", tempfile.gettempdir()):
+        try:
+            if os.path.isdir(base) and shutil.disk_usage(base).free > 2 << 30:
+                return tempfile.mkdtemp(prefix="tcb_bench_", dir=base)
+        except OSError:
+            continue
+    return tempfile.mkdtemp(prefix="tcb_bench_")
+
+
+def time_streamer(tc, prefix, device, steps, warmup, shuffle, barrier):
+    """Batches per second through ZeroCopyTensorStreamer, with a D2H read of a
+    completion word every batch.  Returns (seconds for `steps` batches, h2d bytes, d2h bytes)."""
+    st = tc.ZeroCopyTensorStreamer(prefix, batch_size=SHAPE[0], device=str(device), shuffle=shuffle)
+    token = torch.empty(16, dtype=torch.bfloat16).pin_memory()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    done, started = 0, False
+    total = warmup + steps
+    np.random.seed(1234)
+    while done < total:
+        for batch in st:
+            if done == warmup and not started:
+                torch.cuda.synchronize(device)
+                barrier()
+                ev0.record()
+                started = True
+            token.copy_(batch.view(-1)[-16:], non_blocking=True)  # device -> host, ordered after the decode
+            torch.cuda.current_stream(device).synchronize()
+            done += 1
+            if done == total:
+                break
+    ev1.record()
+    torch.cuda.synchronize(device)
+    barrier()
+    secs = ev0.elapsed_time(ev1) / 1e3
+    h2d = SHAPE[0] * (SHAPE[1] * SHAPE[2] + 3 * (SHAPE[1] * SHAPE[2] // G))
+    st.close()
+    return secs, h2d, token.numel() * 2
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="tcb200", choices=["tcb200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=0, help="batches timed through the streamer (default: min(steps, 200))")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        print(json.dumps({"metric": METRIC, "error": "no CUDA device: this path has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    import tensorcache_b200 as tc
+    from tensorcache_b200 import _lib
+
+    L = _lib.lib()  # raises if the CUDA library is missing
+    numel = int(np.prod(SHAPE))
+    n_sets = 4
+    sets = []
+    for i in range(n_sets):
+        q, s, zp = synthetic_codes(numel, G, 1000 * rank + i, device)
+        sets.append((q, s, zp, torch.empty(SHAPE, dtype=torch.bfloat16, device=device)))
+    stream = torch.cuda.current_stream(device)
+
+    def step(i):
+        q, s, zp, out = sets[i % n_sets]
+        rc = L.tcb_decompress_amo(q.data_ptr(), s.data_ptr(), zp.data_ptr(), out.data_ptr(), numel, G, stream.cuda_stream)
+        if rc != 0:
+            _lib.check(rc)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+    barrier()
+    torch.cuda.synchronize(device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    ev1.record(stream)
+    torch.cuda.synchronize(device)
+    barrier()
+    secs = max_over_ranks(ev0.elapsed_time(ev1) / 1e3)
+    clocks = sampler.stop() if rank == 0 else None
+
+    bytes_per_step = algorithmic_bytes(numel, G)
+    value = bytes_per_step * args.steps * world / secs / 1e9
+    per_gpu = bytes_per_step * args.steps / secs / 1e9
+    peak, peak_kind = peaks()
+
+    # end to end through the reader API: host memory -> GPU bf16 batches
+    e2e_steps = args.e2e_steps or min(args.steps, 200)
+    tmp = scratch_dir()
+    try:
+        prefix = build_cache_shard(tc, tmp, 8 * SHAPE[0], 4000 + rank, device)
+        torch.cuda.synchronize(device)
+        s_contig, h2d, d2h = time_streamer(tc, prefix, device, e2e_steps, args.warmup, False, barrier)
+        s_random, _, _ = time_streamer(tc, prefix, device, e2e_steps, args.warmup, True, barrier)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    s_contig, s_random = max_over_ranks(s_contig), max_over_ranks(s_random)
+    e2e_value = bytes_per_step * e2e_steps * world / s_contig / 1e9
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        from oracle import amo_oracle as orc
+
+        nthreads = orc.default_threads()
+        rate, reps, spent = cpu_decode_rate(numel, G, budget_s=12.0, max_reps=40, nthreads=nthreads)
+        cpu = {"value": rate, "unit": UNIT, "cores": nthreads, "kind": "port",
+               "sample": f"best of {reps} decodes of the full [128,446,768] G32 workload in {spent:.1f} s, "
+                         f"C port of the reference CPU decode, {nthreads} threads"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8->bf16 (fp32 arithmetic)", "data": "synthetic",
+            "config": {"workload": "AMO-BQ G32 decode of [128,446,768] bf16 codes into a preallocated buffer",
+                       "group_size": G, "values_per_step_per_gpu": numel, "algorithmic_bytes_per_step": bytes_per_step,
+                       "l2_policy": f"{n_sets} rotating input/output sets ({n_sets * bytes_per_step / 1e6:.0f} MB) > 126 MB L2",
+                       "parallelism": f"{world} independent replicas, one per GPU, no collective"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "decompress_vec_kernel<G32, 256-bit stores>",
+                         "us_per_launch": secs / args.steps * 1e6},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
+                    "path": "ZeroCopyTensorStreamer, contiguous order, B=128: mmap rows -> pinned -> H2D -> decode -> D2H completion word"},
+            "streamer": {"contiguous_samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
+                         "random_samples_per_s": SHAPE[0] * e2e_steps * world / s_random,
+                         "bf16_equiv_gbs_contiguous": SHAPE[0] * e2e_steps * world * SHAPE[1] * SHAPE[2] * 2 / s_contig / 1e9,
+                         "shard_samples_per_rank": 8 * SHAPE[0], "batch_size": SHAPE[0]},
+            "cpu_baseline": cpu,
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,21 @@
+"""tensorcache_b200: the AMO-BQ feature-cache hot path of TensorCache on NVIDIA B200.
+
+Drop-in for the reference's API on that path -- ``compress`` / ``decompress``,
+``BlockwiseInt8Codec``, ``quantize_int8_amo_bq`` / ``dequantize_int8_amo_bq``,
+``FusedDequantLinear``, ``ZeroCopyTensorStreamer``, ``FeatureCacheWriter`` /
+``FeatureCacheDataset`` -- on hand-written sm_100a CUDA kernels behind a C ABI
+(``include/tcb200.h``, ``libtcb200.so``).  There is no Triton, no backend switch
+and no CPU implementation: without the built library or a CUDA device the
+compute calls raise.
+"""
+from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, quantize_int8_amo_bq
+from .feature_cache import FeatureCacheDataset, FeatureCacheWriter
+from .streamer import ZeroCopyTensorStreamer
+from .utils import compress, decompress, estimate_compression
+
+__version__ = "0.1.0"
+__all__ = [
+    "AMO_BQ_PRESETS", "BlockwiseInt8Codec", "quantize_int8_amo_bq", "dequantize_int8_amo_bq",
+    "compress", "decompress", "estimate_compression",
+    "FeatureCacheWriter", "FeatureCacheDataset", "ZeroCopyTensorStreamer",
+]

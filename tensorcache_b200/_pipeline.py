@@ -1,0 +1,267 @@
+"""Shared host logic of the batch readers: cache manifests, shard maps, and the
+Python handle of the native double-buffered pipeline (``tcb_streamer_*``)."""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+@dataclass
+class ShardFiles:
+    """One file set ``<prefix>_int8.bin / _scales.bin / _zp.bin`` opened read-only."""
+    prefix: str
+    num_samples: int
+    q: Optional[np.memmap] = None      # uint8 [n, seq, dim]
+    s: Optional[np.memmap] = None      # uint16 [n, groups] (bf16 bit patterns)
+    zp: Optional[np.memmap] = None     # uint8 [n, groups]
+
+
+@dataclass
+class CacheLayout:
+    """What a reader needs to know about a cache on disk (Appendix: on-disk format
+    of src/tensorcache/feature_cache.py:85-127, 134-155, 446-540)."""
+    meta: dict
+    seq_len: int
+    dim: int
+    group_size: int
+    amo_bq: bool
+    shards: List[ShardFiles] = field(default_factory=list)
+    total_shards_on_disk: int = 1
+    selected: Optional[List[int]] = None   # shard numbers opened, None = unsharded cache
+
+    @property
+    def groups_per_sample(self) -> int:
+        return (self.seq_len * self.dim + self.group_size - 1) // self.group_size
+
+    @property
+    def num_samples(self) -> int:
+        return sum(s.num_samples for s in self.shards)
+
+    @property
+    def shard_sizes(self) -> List[int]:
+        return [s.num_samples for s in self.shards]
+
+    @property
+    def shard_offsets(self) -> List[int]:
+        off, out = 0, []
+        for s in self.shards:
+            out.append(off)
+            off += s.num_samples
+        return out
+
+    def locate(self, idx: int):
+        """global sample -> (position in self.shards, local row)"""
+        if idx < 0:
+            idx += self.num_samples
+        if not 0 <= idx < self.num_samples:
+            raise IndexError(f"idx {idx} out of range {self.num_samples}")
+        for si, (off, sh) in enumerate(zip(self.shard_offsets, self.shards)):
+            if off <= idx < off + sh.num_samples:
+                return si, idx - off
+        raise IndexError(idx)
+
+    def close(self):
+        for sh in self.shards:
+            for name in ("q", "s", "zp"):
+                mm = getattr(sh, name)
+                if mm is not None and getattr(mm, "_mmap", None) is not None:
+                    try:
+                        mm._mmap.close()
+                    except (BufferError, ValueError):
+                        pass
+                setattr(sh, name, None)
+
+
+def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq: bool) -> ShardFiles:
+    if not amo_bq:
+        raise NotImplementedError("this cache was written with the symmetric INT8 codec; only AMO-BQ caches "
+                                  "(amo_bq=True) are readable on the B200 path")
+    sh = ShardFiles(prefix, n)
+    if n > 0:
+        expect = {"_int8.bin": n * seq_len * dim, "_scales.bin": n * groups * 2, "_zp.bin": n * groups}
+        for suffix, nbytes in expect.items():
+            path = prefix + suffix
+            if not os.path.exists(path):
+                raise FileNotFoundError(f"cache file {path!r} is missing")
+            have = os.path.getsize(path)
+            if have < nbytes:
+                raise ValueError(f"cache file {path!r} is truncated: {have} bytes, {nbytes} needed for {n} samples")
+        sh.q = np.memmap(prefix + "_int8.bin", dtype=np.uint8, mode="r", shape=(n, seq_len, dim))
+        sh.s = np.memmap(prefix + "_scales.bin", dtype=np.uint16, mode="r", shape=(n, groups))
+        sh.zp = np.memmap(prefix + "_zp.bin", dtype=np.uint8, mode="r", shape=(n, groups))
+    return sh
+
+
+def resolve_shards(num_shards: int, shard_idx: Optional[int], rank: Optional[int], world_size: Optional[int],
+                   all_rank_shards: bool) -> Optional[List[int]]:
+    """Which shard numbers a reader opens.  None means "all of them, as one logical cache".
+
+    rank / world_size follow ZeroCopyTensorStreamer (src/tensorcache/streamer.py:69-71):
+    shard ``rank % num_shards``.  With ``all_rank_shards`` a rank instead takes every
+    shard i with ``i % world_size == rank`` -- the two rules agree when
+    ``world_size == num_shards``; the second leaves no shard unread when there are
+    fewer ranks than shards.
+    """
+    if rank is not None and world_size is not None:
+        if shard_idx is not None:
+            raise ValueError("Specify either shard_idx or rank/world_size, not both")
+        if world_size < 1 or not 0 <= rank < world_size:
+            raise ValueError(f"rank {rank} outside world_size {world_size}")
+        if all_rank_shards:
+            return [i for i in range(num_shards) if i % world_size == rank]
+        return [rank % num_shards]
+    if shard_idx is not None:
+        if not 0 <= shard_idx < num_shards:
+            raise ValueError(f"shard_idx {shard_idx} out of range {num_shards}")
+        return [shard_idx]
+    return None
+
+
+def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_rank_shards=False) -> CacheLayout:
+    """Parses ``<prefix>_shards.json`` or ``<prefix>_meta.json`` and maps the files."""
+    prefix = str(cache_prefix)
+    manifest_path = prefix + "_shards.json"
+    if os.path.exists(manifest_path):
+        with open(manifest_path, "r") as f:
+            man = json.load(f)
+        n_shards = man.get("num_shards", len(man.get("shard_prefixes", [])))
+        prefixes = list(man.get("shard_prefixes") or [f"{prefix}_shard{i}" for i in range(n_shards)])
+        # a cache that was moved after it was written: fall back to files beside the manifest
+        for i, p in enumerate(prefixes):
+            if not os.path.exists(p + "_meta.json") and not os.path.exists(p + "_int8.bin"):
+                prefixes[i] = f"{prefix}_shard{i}"
+        selected = resolve_shards(n_shards, shard_idx, rank, world_size, all_rank_shards)
+        seq_len, dim, G = man["seq_len"], man["dim"], man["group_size"]
+        amo = man.get("amo_bq", False)
+        groups = (seq_len * dim + G - 1) // G
+        sizes = list(man.get("shard_sizes") or [])
+        lay = CacheLayout(man, seq_len, dim, G, amo, [], n_shards, selected if selected is not None else list(range(n_shards)))
+        for i in lay.selected:
+            n = None
+            mp = prefixes[i] + "_meta.json"
+            if os.path.exists(mp):
+                with open(mp, "r") as f:
+                    sm = json.load(f)
+                n = sm["num_samples"]
+                if selected is not None and len(selected) == 1:
+                    lay.meta = sm
+            if n is None:
+                n = sizes[i] if sizes else man["num_samples"] // n_shards
+            lay.shards.append(_open_shard(prefixes[i], n, seq_len, dim, groups, amo))
+        return lay
+    # rank / world_size on an unsharded cache are ignored, as the reference's streamer does
+    if shard_idx not in (None, 0):
+        raise ValueError(f"shard_idx {shard_idx} out of range 1")
+    meta_path = prefix + "_meta.json"
+    with open(meta_path, "r") as f:
+        meta = json.load(f)
+    seq_len, dim, G = meta["seq_len"], meta["dim"], meta["group_size"]
+    amo = meta.get("amo_bq", False)
+    groups = (seq_len * dim + G - 1) // G
+    lay = CacheLayout(meta, seq_len, dim, G, amo, [], 1, None)
+    lay.shards.append(_open_shard(prefix, meta["num_samples"], seq_len, dim, groups, amo))
+    return lay
+
+
+def default_gather_threads() -> int:
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return max(1, min(8, n))
+
+
+class NativePipeline:
+    """Owns the ring buffers (torch tensors) and the native streamer handle."""
+
+    def __init__(self, layout: CacheLayout, batch_size: int, device: torch.device, n_slots: int,
+                 n_threads: Optional[int] = None):
+        if device.type != "cuda":
+            raise RuntimeError("the batch readers decode on a CUDA device only (no CPU decode path)")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device available for the batch reader")
+        self.layout = layout
+        self.device = device
+        self.batch_size = int(batch_size)
+        self.n_slots = int(n_slots)
+        vps = layout.seq_len * layout.dim
+        gps = layout.groups_per_sample
+        B = self.batch_size
+        self.pinned_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
+        self.pinned_s = [torch.empty((B, gps), dtype=torch.bfloat16, pin_memory=True) for _ in range(n_slots)]
+        self.pinned_zp = [torch.empty((B, gps), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
+        self.dev_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, device=device) for _ in range(n_slots)]
+        self.dev_s = [torch.empty((B, gps), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
+        self.dev_zp = [torch.empty((B, gps), dtype=torch.uint8, device=device) for _ in range(n_slots)]
+        self.dev_out = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
+
+        def table(tensors):
+            return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+        def base_table(name):
+            return (ctypes.c_void_p * len(layout.shards))(
+                *[(getattr(sh, name).ctypes.data if sh.num_samples > 0 else 0) for sh in layout.shards])
+
+        self._tables = [table(t) for t in (self.pinned_q, self.pinned_s, self.pinned_zp, self.dev_q, self.dev_s, self.dev_zp, self.dev_out)]
+        self._bases = [base_table("q"), base_table("s"), base_table("zp")]
+        self._sizes = (ctypes.c_int64 * len(layout.shards))(*layout.shard_sizes)
+        d = _lib.StreamerDesc()
+        d.n_shards = len(layout.shards)
+        d.q_bases, d.s_bases, d.zp_bases = self._bases
+        d.shard_sizes = self._sizes
+        d.values_per_sample = vps
+        d.groups_per_sample = gps
+        d.group_size = layout.group_size
+        d.batch_size = B
+        d.n_slots = n_slots
+        d.n_threads = n_threads or default_gather_threads()
+        (d.pinned_q, d.pinned_s, d.pinned_zp, d.dev_q, d.dev_s, d.dev_zp, d.dev_out) = self._tables
+        self._handle = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().tcb_streamer_create(ctypes.byref(d), ctypes.byref(self._handle)))
+
+    def begin(self, order: Optional[np.ndarray], n: int) -> None:
+        if order is not None:
+            order = np.ascontiguousarray(order, dtype=np.int64)
+            _lib.check(_lib.lib().tcb_streamer_begin(self._handle, ctypes.c_void_p(order.ctypes.data), int(len(order))))
+        else:
+            _lib.check(_lib.lib().tcb_streamer_begin(self._handle, None, int(n)))
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def next_decoded(self):
+        """(slot, rows); rows == 0 at the end of the pass."""
+        slot, rows = ctypes.c_int(0), ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().tcb_streamer_next(self._handle, self._stream(), ctypes.byref(slot), ctypes.byref(rows)))
+        return slot.value, rows.value
+
+    def acquire(self):
+        slot, rows = ctypes.c_int(0), ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().tcb_streamer_acquire(self._handle, self._stream(), ctypes.byref(slot), ctypes.byref(rows)))
+        return slot.value, rows.value
+
+    def release(self):
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().tcb_streamer_release(self._handle, self._stream()))
+
+    def close(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            _lib.lib().tcb_streamer_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+        for name in ("pinned_q", "pinned_s", "pinned_zp", "dev_q", "dev_s", "dev_zp", "dev_out"):
+            setattr(self, name, None)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

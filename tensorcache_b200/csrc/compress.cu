@@ -1,0 +1,377 @@
+// AMO-BQ encode kernels for sm_100a: per-group asymmetric min/max plus the scale
+// search of the reference's CPU path, reproduced bit for bit.
+//
+// Work split: four lanes ("a quad") per group.  Lane j of the quad owns columns
+// 2j and 2j+1 of every 8-wide vector of the group, i.e. G/4 values in registers.
+// That split is chosen so that the squared-error sum can follow the order of the
+// reference's CPU reduction exactly (8 lanes x 4 partial accumulators per lane,
+// then the 8 lane totals left to right): each GPU lane accumulates its two
+// columns privately in that order and the four lanes chain their totals with
+// warp shuffles.  Min/max use xor-shuffles inside the quad.
+//
+// Exactness rules (src/tensorcache/codec.py:833-893 and :721-771):
+//   every operation is a separate IEEE binary32 operation -- __fdiv_rn / __fmul_rn /
+//   __fadd_rn / __fsub_rn (never contracted into FMA), rintf() for
+//   round-half-to-even, the first minimum wins (strict <), and the candidate
+//   multipliers are the host's torch.linspace values passed in by value.
+// The kernels are ALU-bound (one IEEE division and ~10 dependent operations per
+// value and candidate); they never synchronise with the host.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "tcb_common.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+struct CandTable {
+    float m[64];
+    int n;
+};
+
+__device__ __forceinline__ bool finite_f32(float v) { return (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u; }
+
+__device__ __forceinline__ float clamp255(float v) { return fminf(fmaxf(v, 0.0f), 255.0f); }
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <typename T>
+__device__ __forceinline__ float widen(T v);
+template <>
+__device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float widen<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float widen<float>(float v) { return v; }
+
+// Loads the lane's G/4 values of group `g` (zero-padded past numel), cleans
+// non-finite values to 0 and records which were finite.
+template <int G, typename T>
+__device__ __forceinline__ void load_lane(const T* __restrict__ x, int64_t numel, int64_t base, int j, bool pair_aligned,
+                                          float (&v)[G / 4], uint32_t& finmask) {
+    constexpr int NVEC = G / 8;
+    finmask = 0;
+    const bool whole = base + G <= numel;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+        const int64_t i = base + k * 8 + 2 * j;
+        float a, b;
+        if (whole && pair_aligned) {
+            if (sizeof(T) == 2) {
+                uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(x + i));
+                uint16_t lo = uint16_t(w & 0xffffu), hi = uint16_t(w >> 16);
+                a = widen<T>(*reinterpret_cast<T*>(&lo));
+                b = widen<T>(*reinterpret_cast<T*>(&hi));
+            } else {
+                float2 w = __ldg(reinterpret_cast<const float2*>(x + i));
+                a = w.x;
+                b = w.y;
+            }
+        } else {
+            a = i < numel ? widen<T>(x[i]) : 0.0f;
+            b = i + 1 < numel ? widen<T>(x[i + 1]) : 0.0f;
+        }
+        const bool fa = finite_f32(a), fb = finite_f32(b);
+        v[2 * k] = fa ? a : 0.0f;
+        v[2 * k + 1] = fb ? b : 0.0f;
+        finmask |= (fa ? 1u : 0u) << (2 * k);
+        finmask |= (fb ? 1u : 0u) << (2 * k + 1);
+    }
+}
+
+// Sum of the group's G error terms in the reference's order.  e[2k + a] is the
+// term of element 8k + 2j + a.  Returns the total on every lane of the quad.
+template <int G>
+__device__ __forceinline__ float quad_sum(const float (&e)[G / 4], int j, int lane, uint32_t qmask) {
+    float col[2];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        if (G == 16) {
+            col[a] = __fadd_rn(e[a], e[2 + a]);
+        } else if (G == 32) {
+            col[a] = __fadd_rn(__fadd_rn(__fadd_rn(e[a], e[2 + a]), e[4 + a]), e[6 + a]);
+        } else {  // 64: accumulator i gets vectors i and 4 + i
+            float a0 = __fadd_rn(e[a], e[8 + a]);
+            float a1 = __fadd_rn(e[2 + a], e[10 + a]);
+            float a2 = __fadd_rn(e[4 + a], e[12 + a]);
+            float a3 = __fadd_rn(e[6 + a], e[14 + a]);
+            col[a] = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+        }
+    }
+    // lane totals L0..L7 are added left to right: lane 0 starts, lanes 1..3 continue
+    const int q0 = lane & ~3;
+    float t = __fadd_rn(col[0], col[1]);
+#pragma unroll
+    for (int step = 1; step < 4; ++step) {
+        float prev = __shfl_sync(qmask, t, q0 + step - 1);
+        if (j == step) t = __fadd_rn(__fadd_rn(prev, col[0]), col[1]);
+    }
+    return __shfl_sync(qmask, t, q0 + 3);
+}
+
+__device__ __forceinline__ float quad_min(float v, uint32_t qmask) {
+    v = fminf(v, __shfl_xor_sync(qmask, v, 1));
+    return fminf(v, __shfl_xor_sync(qmask, v, 2));
+}
+__device__ __forceinline__ float quad_max(float v, uint32_t qmask) {
+    v = fmaxf(v, __shfl_xor_sync(qmask, v, 1));
+    return fmaxf(v, __shfl_xor_sync(qmask, v, 2));
+}
+
+template <int G>
+__device__ __forceinline__ void store_codes(uint8_t* __restrict__ q, int64_t numel, int64_t base, int j, bool pair_aligned,
+                                            const uint8_t (&c)[G / 4]) {
+    constexpr int NVEC = G / 8;
+    const bool whole = base + G <= numel;
+#pragma unroll
+    for (int k = 0; k < NVEC; ++k) {
+        const int64_t i = base + k * 8 + 2 * j;
+        if (whole && pair_aligned) {
+            *reinterpret_cast<uint16_t*>(q + i) = uint16_t(c[2 * k]) | (uint16_t(c[2 * k + 1]) << 8);
+        } else {
+            if (i < numel) q[i] = c[2 * k];
+            if (i + 1 < numel) q[i + 1] = c[2 * k + 1];
+        }
+    }
+}
+
+// ---------------------------------------------------------------- legacy presets
+
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                       uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned, bool out_aligned) {
+    constexpr int VPL = G / 4;
+    const int lane = threadIdx.x & 31;
+    const int j = lane & 3;
+    const uint32_t qmask = 0xFu << (lane & ~3);
+    const int64_t quads_per_grid = int64_t(gridDim.x) * (kThreads / 4);
+
+    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 4) + (threadIdx.x >> 2); g < ngroups; g += quads_per_grid) {
+        const int64_t base = g * G;
+        float v[VPL];
+        uint32_t finmask;
+        load_lane<G, T>(x, numel, base, j, in_aligned, v, finmask);
+
+        float lmin = v[0], lmax = v[0];
+#pragma unroll
+        for (int k = 1; k < VPL; ++k) {
+            lmin = fminf(lmin, v[k]);
+            lmax = fmaxf(lmax, v[k]);
+        }
+        const float bmin = quad_min(lmin, qmask);
+        const float bmax = quad_max(lmax, qmask);
+        float rng = fmaxf(__fsub_rn(bmax, bmin), 1e-8f);
+        if (!finite_f32(rng)) rng = 1e-8f;
+        float s0 = __fdiv_rn(rng, 255.0f);
+        if (!finite_f32(s0)) s0 = float(1e-8 / 255.0);
+        const float nbmin = -bmin;
+
+        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
+        for (int c = 0; c < tab.n; ++c) {
+            const float s = __fmul_rn(s0, tab.m[c]);
+            const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
+            float e[VPL];
+#pragma unroll
+            for (int k = 0; k < VPL; ++k) {
+                const float t = __fadd_rn(__fdiv_rn(v[k], s), zp);
+                const float qc = clamp255(rintf(t));
+                const float rec = __fmul_rn(__fsub_rn(qc, zp), s);
+                const float d = ((finmask >> k) & 1u) ? __fsub_rn(v[k], rec) : 0.0f;
+                e[k] = __fmul_rn(d, d);
+            }
+            const float err = quad_sum<G>(e, j, lane, qmask);
+            if (c == 0 || err < best_err) {
+                best_err = err;
+                best_s = s;
+                best_zp = zp;
+            }
+        }
+
+        uint8_t codes[VPL];
+        const uint8_t zp8 = uint8_t(best_zp);
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+            const float t = __fadd_rn(__fdiv_rn(v[k], best_s), best_zp);
+            const float qf = clamp255(rintf(t));
+            codes[k] = ((finmask >> k) & 1u) ? uint8_t(qf) : zp8;
+        }
+        store_codes<G>(q, numel, base, j, out_aligned, codes);
+        if (j == 0) {
+            __nv_bfloat16 sb = __float2bfloat16_rn(best_s);
+            scales[g] = *reinterpret_cast<uint16_t*>(&sb);
+            zps[g] = zp8;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ quality mode
+
+// code choice of the reference's _amo_quality_codes for one value
+__device__ __forceinline__ float quality_code(float x, float s, float zp, float& err_out) {
+    const float r = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
+    float qv = clamp255(r);
+    float d = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(qv, zp), s)));
+    float err = __fmul_rn(d, d);
+    {
+        const float aq = clamp255(__fadd_rn(r, -1.0f));
+        const float ad = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(aq, zp), s)));
+        const float ae = __fmul_rn(ad, ad);
+        if (ae < err) {
+            qv = aq;
+            err = ae;
+        }
+    }
+    {
+        const float aq = clamp255(__fadd_rn(r, 1.0f));
+        const float ad = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(aq, zp), s)));
+        const float ae = __fmul_rn(ad, ad);
+        if (ae < err) {
+            qv = aq;
+            err = ae;
+        }
+    }
+    err_out = err;
+    return qv;
+}
+
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, uint8_t* __restrict__ q,
+                        uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned, bool out_aligned) {
+    constexpr int VPL = G / 4;
+    const int lane = threadIdx.x & 31;
+    const int j = lane & 3;
+    const uint32_t qmask = 0xFu << (lane & ~3);
+    const int64_t quads_per_grid = int64_t(gridDim.x) * (kThreads / 4);
+
+    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 4) + (threadIdx.x >> 2); g < ngroups; g += quads_per_grid) {
+        const int64_t base = g * G;
+        float v[VPL];
+        uint32_t finmask;
+        load_lane<G, T>(x, numel, base, j, in_aligned, v, finmask);
+
+        float lmin = v[0], lmax = v[0];
+#pragma unroll
+        for (int k = 1; k < VPL; ++k) {
+            lmin = fminf(lmin, v[k]);
+            lmax = fmaxf(lmax, v[k]);
+        }
+        const float lower = fminf(quad_min(lmin, qmask), 0.0f);
+        const float upper = fmaxf(quad_max(lmax, qmask), 0.0f);
+        const float scale0 = fmaxf(__fsub_rn(__fdiv_rn(upper, 255.0f), __fdiv_rn(lower, 255.0f)), float(1e-8 / 255.0));
+        const int lo_bits = int(__bfloat16_as_short(__float2bfloat16_rn(__fmul_rn(scale0, 0.85f))));
+        const int hi_bits = int(__bfloat16_as_short(__float2bfloat16_rn(__fmul_rn(scale0, 1.10f))));
+        const float nlower = -lower;
+
+        // Candidates are the bf16 bit patterns lo_bits .. hi_bits.  The reference
+        // enumerates 64 offsets clamped to hi_bits; repeats of hi_bits can never
+        // win under the strict comparison, so the loop stops after the first.
+        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
+        for (int k = 0; k < 64; ++k) {
+            const int bits = lo_bits + k;
+            if (k > 0 && bits > hi_bits) break;
+            const int use = bits < hi_bits ? bits : hi_bits;
+            const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
+            const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
+            float e[VPL];
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                float err;
+                (void)quality_code(v[i], s, zp, err);
+                e[i] = ((finmask >> i) & 1u) ? err : 0.0f;
+            }
+            const float tot = quad_sum<G>(e, j, lane, qmask);
+            if (k == 0 || tot < best_err) {
+                best_err = tot;
+                best_s = s;
+                best_zp = zp;
+            }
+        }
+
+        uint8_t codes[VPL];
+        const uint8_t zp8 = uint8_t(best_zp);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            float err;
+            const float qf = quality_code(v[i], best_s, best_zp, err);
+            codes[i] = ((finmask >> i) & 1u) ? uint8_t(qf) : zp8;
+        }
+        store_codes<G>(q, numel, base, j, out_aligned, codes);
+        if (j == 0) {
+            scales[g] = uint16_t(__float_as_uint(best_s) >> 16);
+            zps[g] = zp8;
+        }
+    }
+}
+
+// -------------------------------------------------------------------- dispatch
+
+template <int G, typename T>
+cudaError_t launch_typed(const void* x, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q, uint16_t* s,
+                         uint8_t* zp, int grid, cudaStream_t st) {
+    const T* xt = static_cast<const T*>(x);
+    const bool in_aligned = (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0;
+    const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
+    if (tab)
+        compress_legacy_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in_aligned, out_aligned);
+    else
+        compress_quality_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in_aligned, out_aligned);
+    return cudaGetLastError();
+}
+
+template <int G>
+cudaError_t launch_g(const void* x, int dtype, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q,
+                     uint16_t* s, uint8_t* zp, int grid, cudaStream_t st) {
+    switch (dtype) {
+    case TCB_DT_BF16: return launch_typed<G, __nv_bfloat16>(x, numel, ngroups, tab, q, s, zp, grid, st);
+    case TCB_DT_F16: return launch_typed<G, __half>(x, numel, ngroups, tab, q, s, zp, grid, st);
+    default: return launch_typed<G, float>(x, numel, ngroups, tab, q, s, zp, grid, st);
+    }
+}
+
+int compress_common(const char* who, const void* x, int dtype, int64_t numel, int group_size, const CandTable* tab,
+                    uint8_t* q, uint16_t* scales, uint8_t* zp, void* stream) {
+    if (numel < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: numel %lld < 0", who, (long long)numel);
+    if (!tcb::group_size_ok(group_size))
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+    if (dtype != TCB_DT_BF16 && dtype != TCB_DT_F16 && dtype != TCB_DT_F32)
+        return tcb::fail(TCB_ERR_BAD_ARG, "%s: dtype %d is not bf16(0) / f16(1) / f32(2)", who, dtype);
+    if (numel == 0) return TCB_OK;
+    if (!x || !q || !scales || !zp) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);
+    const size_t esz = dtype == TCB_DT_F32 ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(x) % esz) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: x not aligned to its element size", who);
+    if (reinterpret_cast<uintptr_t>(scales) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales not 2-byte aligned", who);
+
+    const int64_t ngroups = (numel + group_size - 1) / group_size;
+    const int64_t blocks = (ngroups + kThreads / 4 - 1) / (kThreads / 4);
+    const int64_t max_grid = int64_t(tcb::sm_count()) * 64;
+    const int grid = int(blocks < max_grid ? blocks : max_grid);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    switch (group_size) {
+    case 16: e = launch_g<16>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 32: e = launch_g<32>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    default: e = launch_g<64>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    }
+    return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
+}
+
+}  // namespace
+
+extern "C" int tcb_compress_amo(const void* x, int dtype, int64_t numel, int group_size, const float* multipliers,
+                                int n_cand, uint8_t* q, uint16_t* scales, uint8_t* zp, void* stream) {
+    if (!multipliers) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_compress_amo: multipliers is null");
+    if (n_cand < 1 || n_cand > 64)
+        return tcb::fail(TCB_ERR_TOO_LARGE, "tcb_compress_amo: n_cand %d outside 1..64", n_cand);
+    CandTable tab;
+    for (int i = 0; i < 64; ++i) tab.m[i] = i < n_cand ? multipliers[i] : 0.0f;
+    tab.n = n_cand;
+    return compress_common("tcb_compress_amo", x, dtype, numel, group_size, &tab, q, scales, zp, stream);
+}
+
+extern "C" int tcb_compress_amo_quality(const void* x, int dtype, int64_t numel, int group_size, uint8_t* q,
+                                        uint16_t* scales, uint8_t* zp, void* stream) {
+    return compress_common("tcb_compress_amo_quality", x, dtype, numel, group_size, nullptr, q, scales, zp, stream);
+}

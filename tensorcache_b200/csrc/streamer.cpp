@@ -1,0 +1,468 @@
+// Host side of the batch readers: a multi-threaded row gather (memory-mapped cache
+// shard -> page-locked staging) and the native double-buffered pipeline behind
+// ZeroCopyTensorStreamer / FeatureCacheDataset.iter_batches.
+//
+// Pipeline per batch b (slot = b mod n_slots):
+//   producer thread : wait until the H2D copy that last read pinned[slot] is done
+//                     -> gather rows into pinned[slot] on the worker pool
+//                     -> copy stream waits for the decode that last read
+//                        dev[slot] -> three async H2D copies -> record h2d[slot]
+//   tcb_streamer_next (caller's thread): consumer stream waits for h2d[slot]
+//                     -> decode kernel into out[slot] -> record decoded[slot]
+// The producer runs ahead of the consumer by up to n_slots batches, so the host
+// gather, the PCIe copy and the decode of three different batches overlap.  The
+// reference (src/tensorcache/streamer.py:459-495) has the same ring but runs the
+// gather on the consumer's Python thread and has no event from the decode back
+// to the copy stream nor from the copy back to the host.
+#include <atomic>
+#include <condition_variable>
+#include <cstring>
+#include <functional>
+#include <mutex>
+#include <thread>
+#include <vector>
+
+#include "tcb_common.h"
+
+namespace tcb {
+int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,
+                      int group_size, cudaStream_t st);
+}
+
+namespace {
+
+// Runs fn(task) for task in [0, n) on the calling thread plus up to (n_workers)
+// helper threads; returns when every task has finished.
+class WorkerPool {
+public:
+    explicit WorkerPool(int n_helpers) {
+        for (int i = 0; i < n_helpers; ++i) helpers_.emplace_back([this] { loop(); });
+    }
+    ~WorkerPool() {
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            stop_ = true;
+        }
+        cv_.notify_all();
+        for (auto& t : helpers_) t.join();
+    }
+    void run(int n_tasks, const std::function<void(int)>& fn) {
+        if (n_tasks <= 0) return;
+        {
+            std::lock_guard<std::mutex> lk(mu_);
+            fn_ = &fn;
+            n_tasks_ = n_tasks;
+            next_ = 0;
+            pending_ = n_tasks;
+            ++generation_;
+        }
+        cv_.notify_all();
+        work();
+        std::unique_lock<std::mutex> lk(mu_);
+        done_cv_.wait(lk, [this] { return pending_ == 0; });
+        fn_ = nullptr;
+    }
+    int size() const { return int(helpers_.size()) + 1; }
+
+private:
+    void work() {
+        for (;;) {
+            int t;
+            const std::function<void(int)>* fn;
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                if (!fn_ || next_ >= n_tasks_) return;
+                t = next_++;
+                fn = fn_;
+            }
+            (*fn)(t);
+            {
+                std::lock_guard<std::mutex> lk(mu_);
+                if (--pending_ == 0) done_cv_.notify_all();
+            }
+        }
+    }
+    void loop() {
+        uint64_t seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> lk(mu_);
+                cv_.wait(lk, [&] { return stop_ || generation_ != seen; });
+                if (stop_) return;
+                seen = generation_;
+            }
+            work();
+        }
+    }
+    std::vector<std::thread> helpers_;
+    std::mutex mu_;
+    std::condition_variable cv_, done_cv_;
+    const std::function<void(int)>* fn_ = nullptr;
+    int n_tasks_ = 0, next_ = 0, pending_ = 0;
+    uint64_t generation_ = 0;
+    bool stop_ = false;
+};
+
+// dst row i <- src_of(i), rows split over the pool.  Rows of a cache are hundreds
+// of KB, so one memcpy per row already streams at full speed.
+template <typename SrcOf>
+void gather_rows(WorkerPool& pool, uint8_t* dst, int64_t row_bytes, int64_t n, const SrcOf& src_of) {
+    if (n <= 0 || row_bytes <= 0) return;
+    int parts = pool.size();
+    if (parts > n) parts = int(n);
+    pool.run(parts, [&](int t) {
+        const int64_t lo = n * t / parts, hi = n * (t + 1) / parts;
+        for (int64_t i = lo; i < hi; ++i) std::memcpy(dst + i * row_bytes, src_of(i), size_t(row_bytes));
+    });
+}
+
+WorkerPool& shared_pool(int want) {
+    static std::mutex mu;
+    static WorkerPool* pool = nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!pool || pool->size() < want) {
+        // grown pools replace smaller ones; the old one is drained and joined
+        WorkerPool* old = pool;
+        pool = new WorkerPool(want - 1);
+        delete old;
+    }
+    return *pool;
+}
+
+}  // namespace
+
+extern "C" int tcb_gather_rows(void* dst, const void* src_base, int64_t row_bytes, const int64_t* idx, int64_t first_row,
+                               int64_t n, int nthreads) {
+    if (n < 0 || row_bytes < 0 || first_row < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_gather_rows: negative size");
+    if (n == 0 || row_bytes == 0) return TCB_OK;
+    if (!dst || !src_base) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_gather_rows: null pointer");
+    if (nthreads < 1) nthreads = 1;
+    if (nthreads > 64) nthreads = 64;
+    static std::mutex call_mu;  // the shared pool runs one gather at a time
+    std::lock_guard<std::mutex> lk(call_mu);
+    const uint8_t* src = static_cast<const uint8_t*>(src_base);
+    gather_rows(shared_pool(nthreads), static_cast<uint8_t*>(dst), row_bytes, n,
+                [&](int64_t i) { return src + (idx ? idx[i] : first_row + i) * row_bytes; });
+    return TCB_OK;
+}
+
+// ------------------------------------------------------------------ streamer
+
+struct tcb_streamer {
+    tcb_streamer_desc d{};
+    std::vector<const uint8_t*> q_bases, s_bases, zp_bases;
+    std::vector<int64_t> shard_start;  // first global sample of each shard, plus the total at the end
+    std::vector<void*> pinned_q, pinned_s, pinned_zp, dev_q, dev_s, dev_zp, dev_out;
+    int device = 0;
+    cudaStream_t copy_stream = nullptr;
+    std::vector<cudaEvent_t> h2d_done, released;
+    WorkerPool* pool = nullptr;
+
+    std::thread producer;
+    std::mutex mu;
+    std::condition_variable cv;
+    // pass state (guarded by mu)
+    std::vector<int64_t> order;
+    bool have_order = false;
+    int64_t n_indices = 0, n_batches = 0;
+    int64_t produced = 0;   // batches whose H2D has been enqueued
+    int64_t acquired = 0;   // batches handed to the consumer
+    int64_t consumed = 0;   // batches whose device staging the consumer has released
+    bool pass_active = false;
+    bool producer_idle = true;
+    bool abort_pass = false;
+    bool quit = false;
+    int producer_error = TCB_OK;
+    char producer_msg[256] = "";
+};
+
+namespace {
+
+int64_t batch_rows_of(const tcb_streamer* s, int64_t b) {
+    const int64_t start = b * s->d.batch_size;
+    const int64_t left = s->n_indices - start;
+    return left < s->d.batch_size ? left : s->d.batch_size;
+}
+
+void producer_fail(tcb_streamer* s, cudaError_t e, const char* what) {
+    std::lock_guard<std::mutex> lk(s->mu);
+    s->producer_error = TCB_ERR_CUDA;
+    snprintf(s->producer_msg, sizeof(s->producer_msg), "streamer producer: %s: %s", what, cudaGetErrorString(e));
+    s->cv.notify_all();
+}
+
+// global sample id -> shard and local row
+inline void locate(const tcb_streamer* s, int64_t gid, int& shard, int64_t& local) {
+    int sh = 0;
+    const int n = int(s->shard_start.size()) - 1;
+    while (sh + 1 < n && gid >= s->shard_start[sh + 1]) ++sh;
+    shard = sh;
+    local = gid - s->shard_start[sh];
+}
+
+void producer_main(tcb_streamer* s) {
+    cudaSetDevice(s->device);
+    const int64_t qrow = s->d.values_per_sample;
+    const int64_t srow = s->d.groups_per_sample * 2;
+    const int64_t zrow = s->d.groups_per_sample;
+    for (;;) {
+        {
+            std::unique_lock<std::mutex> lk(s->mu);
+            s->producer_idle = true;
+            s->cv.notify_all();
+            s->cv.wait(lk, [&] { return s->quit || (s->pass_active && !s->abort_pass); });
+            if (s->quit) return;
+            s->producer_idle = false;
+        }
+        for (int64_t b = 0;; ++b) {
+            const int64_t* idx;
+            int64_t first, rows;
+            const int slot = int(b % s->d.n_slots);
+            {
+                std::unique_lock<std::mutex> lk(s->mu);
+                if (b >= s->n_batches) break;
+                // device staging of this slot is free once batch b - n_slots has been released
+                s->cv.wait(lk, [&] { return s->quit || s->abort_pass || s->consumed >= b - s->d.n_slots + 1; });
+                if (s->quit || s->abort_pass) break;
+                rows = batch_rows_of(s, b);
+                first = b * s->d.batch_size;
+                idx = s->have_order ? s->order.data() + first : nullptr;
+            }
+            // The copy that last read this pinned slot must have finished (a no-op for
+            // an event that was never recorded; also covers the previous pass).
+            cudaError_t e = cudaEventSynchronize(s->h2d_done[slot]);
+            if (e != cudaSuccess) { producer_fail(s, e, "cudaEventSynchronize(h2d)"); break; }
+            auto src = [&](const std::vector<const uint8_t*>& bases, int64_t row_bytes) {
+                return [&, row_bytes](int64_t i) {
+                    int sh;
+                    int64_t local;
+                    locate(s, idx ? idx[i] : first + i, sh, local);
+                    return bases[sh] + local * row_bytes;
+                };
+            };
+            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_q[slot]), qrow, rows, src(s->q_bases, qrow));
+            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
+            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+            // the consumer's last read of this device slot (this pass or the one before)
+            e = cudaStreamWaitEvent(s->copy_stream, s->released[slot], 0);
+            if (e != cudaSuccess) { producer_fail(s, e, "cudaStreamWaitEvent(released)"); break; }
+            e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+            if (e == cudaSuccess) e = cudaEventRecord(s->h2d_done[slot], s->copy_stream);
+            if (e != cudaSuccess) { producer_fail(s, e, "H2D enqueue"); break; }
+            {
+                std::lock_guard<std::mutex> lk(s->mu);
+                s->produced = b + 1;
+            }
+            s->cv.notify_all();
+        }
+        {
+            std::lock_guard<std::mutex> lk(s->mu);
+            s->pass_active = false;  // finished, aborted or failed: park until the next begin
+        }
+    }
+}
+
+// Stops the current pass (if any) and waits until the producer is parked and the
+// copy stream is empty.
+int quiesce(tcb_streamer* s) {
+    {
+        std::unique_lock<std::mutex> lk(s->mu);
+        s->abort_pass = true;
+        s->cv.notify_all();
+        s->cv.wait(lk, [&] { return s->producer_idle; });
+        s->pass_active = false;
+        s->abort_pass = false;
+    }
+    TCB_CUDA_TRY(cudaStreamSynchronize(s->copy_stream));
+    return TCB_OK;
+}
+
+}  // namespace
+
+extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer** out) {
+    if (!desc || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null argument");
+    *out = nullptr;
+    if (!tcb::group_size_ok(desc->group_size))
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_streamer_create: group_size %d not in {16, 32, 64}", desc->group_size);
+    if (desc->n_slots < 1 || desc->n_slots > 8) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: n_slots %d outside 1..8", desc->n_slots);
+    if (desc->n_shards < 1 || desc->n_shards > 4096) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: n_shards %d outside 1..4096", desc->n_shards);
+    if (desc->batch_size < 1 || desc->values_per_sample < 1) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: bad sizes");
+    if (desc->groups_per_sample != (desc->values_per_sample + desc->group_size - 1) / desc->group_size)
+        return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: groups_per_sample does not match values_per_sample / group_size");
+    if (desc->values_per_sample % desc->group_size != 0)
+        return tcb::fail(TCB_ERR_BAD_ARG,
+                         "tcb_streamer_create: values per sample (%lld) must be a multiple of the group size so that "
+                         "a batch decodes as one flat tensor", (long long)desc->values_per_sample);
+    if (!desc->q_bases || !desc->s_bases || !desc->zp_bases || !desc->shard_sizes)
+        return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null shard table");
+    for (int i = 0; i < desc->n_shards; ++i) {
+        if (desc->shard_sizes[i] < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: shard %d has negative size", i);
+        if (desc->shard_sizes[i] > 0 && (!desc->q_bases[i] || !desc->s_bases[i] || !desc->zp_bases[i]))
+            return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: shard %d has a null mapping", i);
+    }
+    if (!desc->pinned_q || !desc->pinned_s || !desc->pinned_zp || !desc->dev_q || !desc->dev_s || !desc->dev_zp || !desc->dev_out)
+        return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer table");
+    for (int i = 0; i < desc->n_slots; ++i)
+        if (!desc->pinned_q[i] || !desc->pinned_s[i] || !desc->pinned_zp[i] || !desc->dev_q[i] || !desc->dev_s[i] ||
+            !desc->dev_zp[i] || !desc->dev_out[i])
+            return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer in slot %d", i);
+
+    tcb_streamer* s = new tcb_streamer();
+    s->d = *desc;
+    int64_t total = 0;
+    for (int i = 0; i < desc->n_shards; ++i) {
+        s->q_bases.push_back(static_cast<const uint8_t*>(desc->q_bases[i]));
+        s->s_bases.push_back(static_cast<const uint8_t*>(desc->s_bases[i]));
+        s->zp_bases.push_back(static_cast<const uint8_t*>(desc->zp_bases[i]));
+        s->shard_start.push_back(total);
+        total += desc->shard_sizes[i];
+    }
+    s->shard_start.push_back(total);
+    for (int i = 0; i < desc->n_slots; ++i) {
+        s->pinned_q.push_back(desc->pinned_q[i]);
+        s->pinned_s.push_back(desc->pinned_s[i]);
+        s->pinned_zp.push_back(desc->pinned_zp[i]);
+        s->dev_q.push_back(desc->dev_q[i]);
+        s->dev_s.push_back(desc->dev_s[i]);
+        s->dev_zp.push_back(desc->dev_zp[i]);
+        s->dev_out.push_back(desc->dev_out[i]);
+    }
+    // the caller's tables need not outlive this call
+    s->d.q_bases = s->d.s_bases = s->d.zp_bases = nullptr;
+    s->d.shard_sizes = nullptr;
+    s->d.pinned_q = s->d.pinned_s = s->d.pinned_zp = s->d.dev_q = s->d.dev_s = s->d.dev_zp = s->d.dev_out = nullptr;
+    cudaError_t e = cudaGetDevice(&s->device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s->copy_stream, cudaStreamNonBlocking);
+    for (int i = 0; e == cudaSuccess && i < desc->n_slots; ++i) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        e = cudaEventCreateWithFlags(&a, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b, cudaEventDisableTiming);
+        if (a) s->h2d_done.push_back(a);
+        if (b) s->released.push_back(b);
+    }
+    if (e != cudaSuccess) {
+        int rc = tcb::cuda_fail(e, "tcb_streamer_create");
+        for (auto ev : s->h2d_done) cudaEventDestroy(ev);
+        for (auto ev : s->released) cudaEventDestroy(ev);
+        if (s->copy_stream) cudaStreamDestroy(s->copy_stream);
+        delete s;
+        return rc;
+    }
+    int nt = desc->n_threads < 1 ? 1 : desc->n_threads > 64 ? 64 : desc->n_threads;
+    s->pool = new WorkerPool(nt - 1);
+    s->producer = std::thread(producer_main, s);
+    *out = s;
+    return TCB_OK;
+}
+
+extern "C" int tcb_streamer_num_samples(const tcb_streamer* s, int64_t* out) {
+    if (!s || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_num_samples: null argument");
+    *out = s->shard_start.back();
+    return TCB_OK;
+}
+
+extern "C" int tcb_streamer_begin(tcb_streamer* s, const int64_t* order, int64_t n_indices) {
+    if (!s) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_begin: null streamer");
+    if (n_indices < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_begin: negative count");
+    const int64_t total = s->shard_start.back();
+    if (!order && n_indices > total)
+        return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_begin: %lld samples asked, cache has %lld", (long long)n_indices, (long long)total);
+    if (order)
+        for (int64_t i = 0; i < n_indices; ++i)
+            if (order[i] < 0 || order[i] >= total)
+                return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_begin: index %lld out of range at position %lld", (long long)order[i], (long long)i);
+    int rc = quiesce(s);
+    if (rc != TCB_OK) return rc;
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        if (s->producer_error != TCB_OK) return tcb::fail(s->producer_error, "%s", s->producer_msg);
+        s->have_order = order != nullptr;
+        if (order) s->order.assign(order, order + n_indices); else s->order.clear();
+        s->n_indices = n_indices;
+        s->n_batches = (n_indices + s->d.batch_size - 1) / s->d.batch_size;
+        s->produced = s->acquired = s->consumed = 0;
+        s->pass_active = s->n_batches > 0;
+    }
+    s->cv.notify_all();
+    return TCB_OK;
+}
+
+extern "C" int tcb_streamer_acquire(tcb_streamer* s, void* consumer_stream, int* slot_out, int* rows_out) {
+    if (!s || !slot_out || !rows_out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_acquire: null argument");
+    int64_t b, rows;
+    {
+        std::unique_lock<std::mutex> lk(s->mu);
+        if (s->acquired != s->consumed)
+            return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_acquire: the previous batch has not been released");
+        b = s->acquired;
+        if (b >= s->n_batches) {
+            *slot_out = 0;
+            *rows_out = 0;
+            return TCB_OK;
+        }
+        s->cv.wait(lk, [&] { return s->produced > b || s->producer_error != TCB_OK; });
+        if (s->producer_error != TCB_OK) return tcb::fail(s->producer_error, "%s", s->producer_msg);
+        rows = batch_rows_of(s, b);
+    }
+    const int slot = int(b % s->d.n_slots);
+    TCB_CUDA_TRY(cudaStreamWaitEvent(static_cast<cudaStream_t>(consumer_stream), s->h2d_done[slot], 0));
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        s->acquired = b + 1;
+    }
+    *slot_out = slot;
+    *rows_out = int(rows);
+    return TCB_OK;
+}
+
+extern "C" int tcb_streamer_release(tcb_streamer* s, void* consumer_stream) {
+    if (!s) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_release: null streamer");
+    int64_t b;
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        if (s->acquired != s->consumed + 1) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_release: no batch is acquired");
+        b = s->consumed;
+    }
+    const int slot = int(b % s->d.n_slots);
+    TCB_CUDA_TRY(cudaEventRecord(s->released[slot], static_cast<cudaStream_t>(consumer_stream)));
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        s->consumed = b + 1;
+    }
+    s->cv.notify_all();
+    return TCB_OK;
+}
+
+extern "C" int tcb_streamer_next(tcb_streamer* s, void* consumer_stream, int* slot_out, int* rows_out) {
+    int rc = tcb_streamer_acquire(s, consumer_stream, slot_out, rows_out);
+    if (rc != TCB_OK || *rows_out == 0) return rc;
+    const int slot = *slot_out;
+    rc = tcb::launch_decompress(static_cast<const uint8_t*>(s->dev_q[slot]), static_cast<const uint16_t*>(s->dev_s[slot]),
+                                static_cast<const uint8_t*>(s->dev_zp[slot]), static_cast<uint16_t*>(s->dev_out[slot]),
+                                int64_t(*rows_out) * s->d.values_per_sample, s->d.group_size,
+                                static_cast<cudaStream_t>(consumer_stream));
+    int rc2 = tcb_streamer_release(s, consumer_stream);
+    return rc != TCB_OK ? rc : rc2;
+}
+
+extern "C" int tcb_streamer_destroy(tcb_streamer* s) {
+    if (!s) return TCB_OK;
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        s->quit = true;
+        s->abort_pass = true;
+    }
+    s->cv.notify_all();
+    if (s->producer.joinable()) s->producer.join();
+    cudaStreamSynchronize(s->copy_stream);
+    for (auto ev : s->h2d_done) cudaEventDestroy(ev);
+    for (auto ev : s->released) cudaEventDestroy(ev);
+    cudaStreamDestroy(s->copy_stream);
+    delete s->pool;
+    delete s;
+    return TCB_OK;
+}

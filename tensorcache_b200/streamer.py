@@ -1,0 +1,133 @@
+"""``ZeroCopyTensorStreamer``: ring-buffered batch reader over an AMO-BQ feature cache.
+
+Same constructor, iteration protocol and public attributes as the reference class
+(src/tensorcache/streamer.py:19-587).  The work happens in the native pipeline
+(``tcb_streamer_*``): gather threads copy rows from the memory-mapped shard into
+page-locked staging, a copy stream moves them to the GPU, and the decode kernel
+runs on the caller's current stream, all overlapped across ring slots.
+
+Differences from the reference, on purpose:
+* the ring is ordered by events in both directions (the reference lets the host
+  and the copy stream overwrite buffers that may still be in use);
+* the decode device must be CUDA (the reference's ``device="cpu"`` branch is a
+  CPU implementation, which this package does not have); the host-side parts
+  (manifest, rank -> shard mapping, ``len``) work without a GPU;
+* ``all_rank_shards=True`` lets a rank read every shard ``i`` with
+  ``i % world_size == rank`` instead of the single shard ``rank % num_shards``.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Iterator, Optional, Union
+
+import numpy as np
+import torch
+
+from ._pipeline import NativePipeline, open_cache
+
+
+class ZeroCopyTensorStreamer:
+    def __init__(
+        self,
+        cache_prefix: Union[str, Path],
+        batch_size: int = 128,
+        device: str = "cuda:0",
+        shuffle: bool = True,
+        low_vram: bool = False,
+        shard_idx: Optional[int] = None,
+        rank: Optional[int] = None,
+        world_size: Optional[int] = None,
+        all_rank_shards: bool = False,
+        gather_threads: Optional[int] = None,
+    ):
+        self.cache_prefix = Path(cache_prefix)
+        self.batch_size = int(batch_size)
+        self.device = torch.device(device)
+        self.shuffle = shuffle
+        self.low_vram = low_vram
+        self.rank = rank
+        self.world_size = world_size
+        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards)
+        lay = self._layout
+        self.meta = lay.meta
+        self.is_sharded = lay.selected is not None and len(lay.shards) > 1
+        self.num_shards = len(lay.shards)
+        self.shard_idx = lay.selected[0] if lay.selected is not None and len(lay.selected) == 1 and (
+            shard_idx is not None or rank is not None) else shard_idx
+        self.shard_prefixes = [s.prefix for s in lay.shards]
+        self.shard_sizes = lay.shard_sizes
+        self.shard_offsets = lay.shard_offsets
+        self.num_samples = lay.num_samples
+        self.seq_len = lay.seq_len
+        self.dim = lay.dim
+        self.group_size = lay.group_size
+        self.amo_bq = lay.amo_bq
+        self.scales_per_sample = lay.groups_per_sample
+        self.n_bufs = 1 if low_vram else 2
+        self.indices = np.arange(self.num_samples)
+        self._gather_threads = gather_threads
+        self._pipe: Optional[NativePipeline] = None
+        self._closed = False
+        self.out_bf16 = None
+        self.out_bf16_0 = self.out_bf16_1 = None
+        if self.device.type == "cuda" and torch.cuda.is_available():
+            self._ensure_pipeline()
+
+    # -- host-side helpers -------------------------------------------------
+    def __len__(self) -> int:
+        return (self.num_samples + self.batch_size - 1) // self.batch_size
+
+    def __enter__(self) -> "ZeroCopyTensorStreamer":
+        return self
+
+    def __exit__(self, exc_type, exc_val, exc_tb) -> None:
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ensure_pipeline(self) -> NativePipeline:
+        if self._closed:
+            raise RuntimeError("streamer is closed")
+        if self._pipe is None:
+            self._pipe = NativePipeline(self._layout, self.batch_size, self.device, self.n_bufs, self._gather_threads)
+            self.out_bf16 = self._pipe.dev_out
+            self.out_bf16_0 = self.out_bf16[0]
+            self.out_bf16_1 = self.out_bf16[-1]
+            self.gpu_int8, self.gpu_scales, self.gpu_zp = self._pipe.dev_q, self._pipe.dev_s, self._pipe.dev_zp
+            self.pinned_int8, self.pinned_scales, self.pinned_zp = self._pipe.pinned_q, self._pipe.pinned_s, self._pipe.pinned_zp
+        return self._pipe
+
+    # -- iteration -----------------------------------------------------------
+    def __iter__(self) -> Iterator[torch.Tensor]:
+        """Yields bf16 ``[rows, seq_len, dim]`` views into the output ring.  A view
+        stays valid until ``n_bufs`` further batches have been requested; clone it
+        to keep it longer.  Shuffling uses numpy's global RNG, like the reference."""
+        pipe = self._ensure_pipeline()
+        if self.shuffle:
+            np.random.shuffle(self.indices)
+            pipe.begin(self.indices, self.num_samples)
+        else:
+            pipe.begin(None, self.num_samples)
+        while True:
+            slot, rows = pipe.next_decoded()
+            if rows == 0:
+                return
+            yield pipe.dev_out[slot][:rows]
+
+    def close(self):
+        if getattr(self, "_closed", True):
+            return
+        self._closed = True
+        if self._pipe is not None:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize(self.device)
+            self._pipe.close()
+            self._pipe = None
+        self.out_bf16 = self.out_bf16_0 = self.out_bf16_1 = None
+        self.gpu_int8 = self.gpu_scales = self.gpu_zp = None
+        self.pinned_int8 = self.pinned_scales = self.pinned_zp = None
+        self._layout.close()

@@ -1,0 +1,75 @@
+"""C-ABI checks that need no GPU: the library loads, exports every symbol the
+header declares, validates arguments before touching the device, and its
+host-side row gather works."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "tcb200.h").read_text()
+    return sorted(set(re.findall(r"TCB_API\s+[\w\s\*]+?\b(tcb_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_surface():
+    names = declared_symbols()
+    for must in ("tcb_decompress_amo", "tcb_compress_amo", "tcb_compress_amo_quality", "tcb_gather_rows",
+                 "tcb_streamer_create", "tcb_streamer_next", "tcb_last_error", "tcb_version"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from tensorcache_b200 import _lib
+
+    for name in declared_symbols():
+        assert hasattr(built_lib, name), f"{name} declared in include/tcb200.h but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature in tensorcache_b200/_lib.py"
+    assert built_lib.tcb_version() == 100
+
+
+def test_argument_validation_happens_before_any_device_work(built_lib):
+    from tensorcache_b200 import _lib
+
+    L = built_lib
+    assert L.tcb_decompress_amo(None, None, None, None, 0, 32, None) == _lib.TCB_OK            # empty is fine
+    assert L.tcb_decompress_amo(None, None, None, None, 10, 24, None) == _lib.ERR_GROUP_SIZE
+    assert b"group_size 24" in L.tcb_last_error()
+    assert L.tcb_decompress_amo(None, None, None, None, -1, 32, None) == _lib.ERR_BAD_ARG
+    assert L.tcb_decompress_amo(None, None, None, None, 10, 32, None) == _lib.ERR_BAD_ARG       # null pointers
+    m = (ctypes.c_float * 4)(1, 1, 1, 1)
+    assert L.tcb_compress_amo(None, 0, 10, 32, m, 0, None, None, None, None) == _lib.ERR_TOO_LARGE
+    assert L.tcb_compress_amo(None, 0, 10, 32, m, 65, None, None, None, None) == _lib.ERR_TOO_LARGE
+    assert L.tcb_compress_amo(None, 0, 10, 32, None, 4, None, None, None, None) == _lib.ERR_BAD_ARG
+    assert L.tcb_compress_amo(None, 7, 10, 32, m, 4, None, None, None, None) == _lib.ERR_BAD_ARG  # dtype
+    assert L.tcb_compress_amo_quality(None, 0, 10, 48, None, None, None, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_compress_amo_quality(None, 0, 0, 16, None, None, None, None) == _lib.TCB_OK
+    with pytest.raises(ValueError):
+        _lib.check(_lib.ERR_GROUP_SIZE)
+
+
+@pytest.mark.parametrize("nthreads", [1, 3, 8])
+def test_gather_rows(built_lib, nthreads):
+    rng = np.random.default_rng(0)
+    src = rng.integers(0, 256, (50, 1000), dtype=np.uint8)
+    idx = rng.permutation(50)[:17].astype(np.int64)
+    dst = np.zeros((17, 1000), np.uint8)
+    assert built_lib.tcb_gather_rows(dst.ctypes.data, src.ctypes.data, 1000, idx.ctypes.data, 0, 17, nthreads) == 0
+    assert np.array_equal(dst, src[idx])
+    dst2 = np.zeros((20, 1000), np.uint8)
+    assert built_lib.tcb_gather_rows(dst2.ctypes.data, src.ctypes.data, 1000, None, 30, 20, nthreads) == 0
+    assert np.array_equal(dst2, src[30:50])
+    assert built_lib.tcb_gather_rows(dst2.ctypes.data, src.ctypes.data, 1000, None, 0, 0, nthreads) == 0
+    assert built_lib.tcb_gather_rows(None, src.ctypes.data, 1000, None, 0, 5, nthreads) != 0
+
+
+def test_product_package_does_not_touch_the_oracle():
+    """The oracle is test infrastructure; nothing under tensorcache_b200/ may import it."""
+    for p in (ROOT / "tensorcache_b200").rglob("*.py"):
+        text = p.read_text()
+        assert "oracle" not in text.replace("oracle/", ""), f"{p} mentions the oracle"
+        assert "import triton" not in text and "torch.compile" not in text

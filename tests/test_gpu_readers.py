@@ -1,0 +1,134 @@
+"""Writer / reader parity on the GPU: files byte-identical with the reference
+writer's, batches bit-identical with decompress of the same codes."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import tensorcache_b200 as tc
+from tests import synth
+from tests.util import bits, from_bits
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+DEV = "cuda:0"
+
+
+def _features(golden_rows):
+    return from_bits(golden_rows["features"]).view(7, 6, 64)
+
+
+@pytest.mark.parametrize("sub,kw", [("cache_single", dict(group_size=32, amo_mode="balanced")),
+                                    ("cache_sharded", dict(group_size=16, amo_mode="quality", num_shards=3))])
+def test_writer_output_is_byte_identical_with_the_reference_writer(tmp_path, golden_rows, sub, kw):
+    feats = _features(golden_rows)
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 7, 6, 64, amo_bq=True, **kw)
+    w.append(feats[:3].to(DEV))       # CUDA batch
+    w.append(feats[3])                # single CPU sample
+    w.append(feats[4:])               # CPU batch
+    with pytest.raises(ValueError):
+        w.append(feats[0])            # past capacity
+    w.close()
+    w.close()                          # idempotent
+    for ref_file in sorted((GOLDEN / sub).iterdir()):
+        mine = tmp_path / ref_file.name
+        assert mine.exists(), ref_file.name
+        if ref_file.suffix == ".bin":
+            assert mine.read_bytes() == ref_file.read_bytes(), ref_file.name
+        else:
+            a, b = json.loads(mine.read_text()), json.loads(ref_file.read_text())
+            for k in ("shard_prefixes", "shard_metas"):   # path strings differ by construction
+                a.pop(k, None), b.pop(k, None)
+            assert a == b, ref_file.name
+
+
+def test_open_append_continues_a_cache(tmp_path, golden_rows):
+    feats = _features(golden_rows)
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 4, 6, 64, group_size=32, amo_bq=True, amo_mode="balanced")
+    w.append(feats[:4]); w.close()
+    with pytest.raises(ValueError):
+        tc.FeatureCacheWriter.open_append(tmp_path / "feat", 3, group_size=16)
+    w = tc.FeatureCacheWriter.open_append(tmp_path / "feat", 3, group_size=32)
+    w.append(feats[4:].to(DEV)); w.close()
+    for name in ("feat_int8.bin", "feat_scales.bin", "feat_zp.bin"):
+        assert (tmp_path / name).read_bytes() == (GOLDEN / "cache_single" / name).read_bytes()
+    assert json.loads((tmp_path / "feat_meta.json").read_text())["num_samples"] == 7
+
+
+@pytest.mark.parametrize("sub", ["cache_single", "cache_sharded"])
+def test_readers_on_reference_written_caches(golden_rows, sub):
+    want = np.concatenate([golden_rows[f"{sub}/{i}/rec"] for i in range(7)])
+    prefix = GOLDEN / sub / "feat"
+    # ring streamer, contiguous, B=2 -> partial last batch
+    with tc.ZeroCopyTensorStreamer(prefix, batch_size=2, device=DEV, shuffle=False) as st:
+        assert len(st) == 4 and st.out_bf16_0 is not None
+        for _ in range(2):            # re-iterable
+            got = [b.clone() for b in st]
+            assert [g.shape[0] for g in got] == [2, 2, 2, 1]
+            assert np.array_equal(bits(torch.cat(got)), want)
+    # low_vram (single slot) and a batch larger than the cache
+    with tc.ZeroCopyTensorStreamer(prefix, batch_size=16, device=DEV, shuffle=False, low_vram=True) as st:
+        got = [b.clone() for b in st]
+        assert len(got) == 1 and np.array_equal(bits(got[0]), want)
+    # shuffled: every sample exactly once
+    np.random.seed(3)
+    with tc.ZeroCopyTensorStreamer(prefix, batch_size=3, device=DEV, shuffle=True) as st:
+        got = torch.cat([b.clone() for b in st])
+        order = st.indices.copy()
+    per = want.reshape(7, -1)
+    assert sorted(order.tolist()) == list(range(7))
+    assert np.array_equal(bits(got).reshape(7, -1), per[order])
+    # dataset: iter_batches (decoded and raw), auto_dequant_device
+    ds = tc.FeatureCacheDataset(prefix, auto_dequant_device=DEV)
+    assert np.array_equal(bits(ds[2]), golden_rows[f"{sub}/2/rec"])
+    got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=4, shuffle=False, device=DEV)])
+    assert np.array_equal(bits(got), want)
+    raw = list(ds.iter_batches(batch_size=4, shuffle=False, device=DEV, dequantize=False))
+    assert len(raw) == 2 and raw[0][0].shape == (4, 6, 64) and raw[1][0].shape == (3, 6, 64)
+    q = torch.cat([r[0] for r in raw]).cpu().numpy().reshape(7, -1)
+    assert np.array_equal(q, np.stack([golden_rows[f"{sub}/{i}/q"].reshape(-1) for i in range(7)]))
+    rec = tc.decompress(torch.cat([r[0] for r in raw]), torch.cat([r[1] for r in raw]), (7, 6, 64),
+                        torch.cat([r[2] for r in raw]), ds.group_size)
+    assert np.array_equal(bits(rec), want)
+    ds.close()
+
+
+def test_rank_sharding_on_the_gpu(golden_rows):
+    prefix = GOLDEN / "cache_sharded" / "feat"
+    with tc.ZeroCopyTensorStreamer(prefix, batch_size=2, device=DEV, shuffle=False, rank=1, world_size=3) as st:
+        got = torch.cat([b.clone() for b in st])
+    assert np.array_equal(bits(got), golden_rows["cache_sharded/rank1_of_3/rec"])
+    seen = []
+    for r in range(2):   # two ranks over three shards, every shard read once
+        with tc.ZeroCopyTensorStreamer(prefix, batch_size=4, device=DEV, shuffle=False, rank=r, world_size=2, all_rank_shards=True) as st:
+            seen.append(bits(torch.cat([b.clone() for b in st])).reshape(st.num_samples, -1))
+    rows = {i: golden_rows[f"cache_sharded/{i}/rec"] for i in range(7)}
+    assert np.array_equal(seen[0], np.stack([rows[i] for i in (0, 1, 2, 5, 6)]))
+    assert np.array_equal(seen[1], np.stack([rows[i] for i in (3, 4)]))
+
+
+def test_larger_cache_round_trip_and_early_exit(tmp_path):
+    """2 shards x 160 samples of [32, 256]; contiguous and shuffled passes, abandoning a pass midway."""
+    x = synth.config0_style(40, (320, 32, 256))
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 320, 32, 256, group_size=32, amo_bq=True, amo_mode="fast", num_shards=2)
+    for i in range(0, 320, 100):
+        w.append(x[i:i + 100].to(DEV))
+    w.close()
+    q, s, zp, _ = tc.compress(x.to(DEV), "fast", 32)
+    want = bits(tc.decompress(q, s, (320, 32, 256), zp, 32)).reshape(320, -1)
+    with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=48, device=DEV, shuffle=False, gather_threads=4) as st:
+        assert st.num_samples == 320 and len(st) == 7
+        it = iter(st)
+        next(it); next(it)            # leave the pass after two batches
+        del it
+        got = bits(torch.cat([b.clone() for b in st])).reshape(320, -1)
+        assert np.array_equal(got, want)
+        st.shuffle = True
+        np.random.seed(11)
+        got = bits(torch.cat([b.clone() for b in st])).reshape(320, -1)
+        assert np.array_equal(got, want[st.indices])
+    with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False, shard_idx=1) as st:
+        got = bits(torch.cat([b.clone() for b in st])).reshape(160, -1)
+        assert np.array_equal(got, want[160:])
