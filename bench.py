@@ -50,6 +50,11 @@ G = 32
 METRIC = "amo_bq_g32_dequant_throughput"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one isolated launch of this workload
+# (profiles/decompress_v8_kernel_G32_128x446x768.md): 48.03 MB read + 35.9 MB written.
+DRAM_TRAFFIC_PER_LAUNCH = 83.9e6
+TRAFFIC_NOTE = ("bytes per launch from one ncu capture: reads 48.03 MB = algorithmic reads; of the 87.69 MB stored only "
+                "35.9 MB reach DRAM inside an isolated launch, the rest is written back from L2 afterwards")
 
 
 def algorithmic_bytes(numel: int, g: int) -> float:
@@ -142,7 +147,7 @@ def physical_gpu_index(local_index: int) -> int:
 # --------------------------------------------------------------------------- CPU
 
 def cpu_decode_rate(numel: int, g: int, budget_s: float, max_reps: int, nthreads: int):
-    """Best-of rate of the C port of the reference CPU decode; returns (GB/s, reps, seconds)."""
+    """Sustained rate of the C port of the reference CPU decode; returns (GB/s, reps, seconds)."""
     from oracle import amo_oracle as orc
 
     rng = np.random.default_rng(0)
@@ -151,13 +156,12 @@ def cpu_decode_rate(numel: int, g: int, budget_s: float, max_reps: int, nthreads
     s = torch.exp(torch.rand(numel // g) * 6.0 - 7.0).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     out = np.empty(numel, np.uint16)
     orc.decompress(q, s, zp, g, nthreads=nthreads, out=out)  # warm-up, page-faults the output
-    best, reps, t_start = float("inf"), 0, time.perf_counter()
+    reps, t_start = 0, time.perf_counter()
     while reps < max_reps and time.perf_counter() - t_start < budget_s:
-        t0 = time.perf_counter()
         orc.decompress(q, s, zp, g, nthreads=nthreads, out=out)
-        best = min(best, time.perf_counter() - t0)
         reps += 1
-    return algorithmic_bytes(numel, g) / best / 1e9, reps, time.perf_counter() - t_start
+    spent = time.perf_counter() - t_start
+    return algorithmic_bytes(numel, g) * reps / spent / 1e9, reps, spent
 
 
 def run_reference_arm(args):
@@ -269,6 +273,7 @@ def main():
     ap.add_argument("--impl", default="tcb200", choices=["tcb200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=0, help="batches timed through the streamer (default: min(steps, 200))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="skip the streamer / e2e leg (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -332,7 +337,6 @@ def main():
     torch.cuda.synchronize(device)
     barrier()
     secs = max_over_ranks(ev0.elapsed_time(ev1) / 1e3)
-    clocks = sampler.stop() if rank == 0 else None
 
     bytes_per_step = algorithmic_bytes(numel, G)
     value = bytes_per_step * args.steps * world / secs / 1e9
@@ -341,25 +345,31 @@ def main():
 
     # end to end through the reader API: host memory -> GPU bf16 batches
     e2e_steps = args.e2e_steps or min(args.steps, 200)
-    tmp = scratch_dir()
-    try:
-        prefix = build_cache_shard(tc, tmp, 8 * SHAPE[0], 4000 + rank, device)
-        torch.cuda.synchronize(device)
-        s_contig, h2d, d2h = time_streamer(tc, prefix, device, e2e_steps, args.warmup, False, barrier)
-        s_random, _, _ = time_streamer(tc, prefix, device, e2e_steps, args.warmup, True, barrier)
-    finally:
-        shutil.rmtree(tmp, ignore_errors=True)
-    s_contig, s_random = max_over_ranks(s_contig), max_over_ranks(s_random)
-    e2e_value = bytes_per_step * e2e_steps * world / s_contig / 1e9
+    if args.decode_only:
+        s_contig = s_random = float("nan")
+        h2d = d2h = 0
+    else:
+        tmp = scratch_dir()
+        try:
+            prefix = build_cache_shard(tc, tmp, 8 * SHAPE[0], 4000 + rank, device)
+            torch.cuda.synchronize(device)
+            s_contig, h2d, d2h = time_streamer(tc, prefix, device, e2e_steps, args.warmup, False, barrier)
+            s_random, _, _ = time_streamer(tc, prefix, device, e2e_steps, args.warmup, True, barrier)
+        finally:
+            shutil.rmtree(tmp, ignore_errors=True)
+        s_contig, s_random = max_over_ranks(s_contig), max_over_ranks(s_random)
+    e2e_value = None if args.decode_only else bytes_per_step * e2e_steps * world / s_contig / 1e9
+
+    clocks = sampler.stop() if rank == 0 else None   # sampled over the decode loop and the streamer passes
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
         from oracle import amo_oracle as orc
 
         nthreads = orc.default_threads()
-        rate, reps, spent = cpu_decode_rate(numel, G, budget_s=12.0, max_reps=40, nthreads=nthreads)
+        rate, reps, spent = cpu_decode_rate(numel, G, budget_s=12.0, max_reps=5000, nthreads=nthreads)
         cpu = {"value": rate, "unit": UNIT, "cores": nthreads, "kind": "port",
-               "sample": f"best of {reps} decodes of the full [128,446,768] G32 workload in {spent:.1f} s, "
+               "sample": f"{reps} back-to-back decodes of the full [128,446,768] G32 workload in {spent:.1f} s, "
                          f"C port of the reference CPU decode, {nthreads} threads"}
 
     if rank == 0:
@@ -372,15 +382,17 @@ def main():
                        "l2_policy": f"{n_sets} rotating input/output sets ({n_sets * bytes_per_step / 1e6:.0f} MB) > 126 MB L2",
                        "parallelism": f"{world} independent replicas, one per GPU, no collective"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "decompress_vec_kernel<G32, 256-bit stores>",
+                         "traffic": DRAM_TRAFFIC_PER_LAUNCH, "traffic_note": TRAFFIC_NOTE, "peak_kind": peak_kind, "kernel": "decompress_v8_kernel<G32>",
                          "us_per_launch": secs / args.steps * 1e6},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
-                    "path": "ZeroCopyTensorStreamer, contiguous order, B=128: mmap rows -> pinned -> H2D -> decode -> D2H completion word"},
-            "streamer": {"contiguous_samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
-                         "random_samples_per_s": SHAPE[0] * e2e_steps * world / s_random,
-                         "bf16_equiv_gbs_contiguous": SHAPE[0] * e2e_steps * world * SHAPE[1] * SHAPE[2] * 2 / s_contig / 1e9,
-                         "shard_samples_per_rank": 8 * SHAPE[0], "batch_size": SHAPE[0]},
+            "e2e": None if args.decode_only else {
+                "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
+                "path": "ZeroCopyTensorStreamer, contiguous order, B=128: mmap rows -> pinned -> H2D -> decode -> D2H completion word"},
+            "streamer": None if args.decode_only else {
+                "contiguous_samples_per_s": SHAPE[0] * e2e_steps * world / s_contig,
+                "random_samples_per_s": SHAPE[0] * e2e_steps * world / s_random,
+                "bf16_equiv_gbs_contiguous": SHAPE[0] * e2e_steps * world * SHAPE[1] * SHAPE[2] * 2 / s_contig / 1e9,
+                "shard_samples_per_rank": 8 * SHAPE[0], "batch_size": SHAPE[0]},
             "cpu_baseline": cpu,
             "gpu_launches": args.steps,
             "clocks": clocks,

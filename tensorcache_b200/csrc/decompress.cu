@@ -1,14 +1,21 @@
 // AMO-BQ decode kernel for sm_100a:  out = bf16((q - zp) * scale) per group of G codes.
 //
 // The kernel is HBM-bound (1 + 3/G bytes read and 2 bytes written per value), so
-// the design is about bytes in flight and full-width transactions:
-//   - each thread owns 16 consecutive codes: one 128-bit load of codes, one bf16
-//     scale and one zero point (read once per chunk, never per element), and one
-//     256-bit store of 16 bf16 values (two 128-bit stores when `out` is only
-//     16-byte aligned);
-//   - UNROLL independent chunks per thread are loaded before any is converted,
-//     so every SM keeps tens of KB of loads outstanding;
-//   - the grid is a multiple of the SM count and strides over tiles.
+// the design is about bytes in flight, full-width transactions and L2 policy:
+//   - each thread owns 32 consecutive codes: one 256-bit load of codes, the bf16
+//     scale(s) and zero point(s) of those codes (read once, never per element), and
+//     two 256-bit stores of 16 bf16 values each; a warp instruction therefore moves
+//     1 KB of contiguous memory and every store fills whole 32-byte sectors;
+//   - codes and output are streamed once, so loads and stores carry the
+//     L2::evict_first policy -- without it the 88 MB of output written per call
+//     pushes dirty lines through L2 in LRU order and costs ~8 % of the bandwidth;
+//   - UNROLL independent loads per thread are issued before any is converted;
+//   - the grid is exactly one wave (occupancy x SM count) and every block owns an
+//     equal contiguous share of the input;
+//   - launches opt into programmatic dependent launch, so back-to-back decodes on
+//     one stream overlap the next launch's scheduling with this one's tail.
+// Pointers that are only 16-byte aligned take a 128-bit variant of the same
+// kernel, anything else an element-wise kernel; all three compute the same bits.
 // Arithmetic: a code byte is spliced into the mantissa of 2^23 (one PRMT), the
 // subtraction of (2^23 + zp) yields the exact integer q - zp, and its product with
 // a bf16 scale has at most 16 significant bits, so the fp32 product is exact and
@@ -29,12 +36,6 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const uint4* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
-}
-
-__device__ __forceinline__ void stg_v8(uint16_t* p, const uint32_t (&o)[8]) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(o[0]), "r"(o[1]),
-                 "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
-                 : "memory");
 }
 
 __device__ __forceinline__ void stg_v4x2(uint16_t* p, const uint32_t (&o)[8]) {
@@ -67,24 +68,112 @@ __device__ __forceinline__ uint16_t decode_one(uint8_t code, uint8_t z, uint16_t
     return *reinterpret_cast<uint16_t*>(&b);
 }
 
-// LOG2_CPG: log2(chunks of 16 codes per group) = log2(G / 16)
-template <int LOG2_CPG, bool STORE256>
+__device__ __forceinline__ void ldg_stream_v8(const uint8_t* p, uint32_t (&w)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+
+__device__ __forceinline__ void stg_stream_v8(uint16_t* p, const uint32_t (&o)[8]) {
+    asm volatile("st.global.L2::evict_first.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(o[0]), "r"(o[1]),
+                 "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                 : "memory");
+}
+
+constexpr int kUnroll32 = 2;
+
+// Main kernel: 32 codes per thread.  LOG2_G = log2(group size) in {4, 5, 6}.
+// Needs q and out 32-byte aligned.  Every block owns one contiguous, equally
+// sized range of 32-code units; the grid is exactly the number of blocks the
+// device holds at once, so there is a single wave and no block does more work
+// than another.
+template <int LOG2_G>
+__global__ void __launch_bounds__(kThreads)
+decompress_v8_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales,
+                     const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel) {
+    // Programmatic dependent launch: let the next kernel of the stream get
+    // scheduled while this one drains, and do not touch memory before the
+    // previous kernel of the stream has completed and flushed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int64_t units = numel >> 5;
+    const int64_t begin = units * blockIdx.x / gridDim.x;
+    const int64_t end = units * (blockIdx.x + 1) / gridDim.x;
+
+    for (int64_t t0 = begin + threadIdx.x; t0 < end; t0 += int64_t(kThreads) * kUnroll32) {
+        uint32_t w[kUnroll32][8];
+        uint16_t sb[kUnroll32][2];
+        uint8_t zb[kUnroll32][2];
+#pragma unroll
+        for (int u = 0; u < kUnroll32; ++u) {
+            const int64_t t = t0 + int64_t(u) * kThreads;
+            if (t < end) {
+                ldg_stream_v8(q + (t << 5), w[u]);
+                if (LOG2_G == 4) {  // two groups of 16 per unit
+                    sb[u][0] = __ldg(scales + 2 * t);
+                    sb[u][1] = __ldg(scales + 2 * t + 1);
+                    zb[u][0] = __ldg(zp + 2 * t);
+                    zb[u][1] = __ldg(zp + 2 * t + 1);
+                } else {  // one group (G32) or half a group (G64)
+                    const int64_t g = t >> (LOG2_G - 5);
+                    sb[u][0] = sb[u][1] = __ldg(scales + g);
+                    zb[u][0] = zb[u][1] = __ldg(zp + g);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll32; ++u) {
+            const int64_t t = t0 + int64_t(u) * kThreads;
+            if (t < end) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float scale = bf16_bits_to_float(sb[u][h]);
+                    const float zmagic = 8388608.0f + float(zb[u][h]);
+                    uint32_t o[8];
+                    convert_word(w[u][4 * h + 0], zmagic, scale, o[0], o[1]);
+                    convert_word(w[u][4 * h + 1], zmagic, scale, o[2], o[3]);
+                    convert_word(w[u][4 * h + 2], zmagic, scale, o[4], o[5]);
+                    convert_word(w[u][4 * h + 3], zmagic, scale, o[6], o[7]);
+                    stg_stream_v8(out + (t << 5) + 16 * h, o);
+                }
+            }
+        }
+    }
+
+    // ragged tail: numel % 32 codes, handled by the first threads of block 0
+    const int tail = int(numel & 31);
+    if (blockIdx.x == 0 && threadIdx.x < tail) {
+        const int64_t i = (units << 5) + threadIdx.x;
+        const int64_t g = i >> LOG2_G;
+        out[i] = decode_one(q[i], zp[g], scales[g]);
+    }
+}
+
+// Variant for pointers that are 16- but not 32-byte aligned: 16 codes per thread,
+// 128-bit load, two 128-bit stores.  LOG2_CPG = log2(G / 16).
+template <int LOG2_CPG>
 __global__ void __launch_bounds__(kThreads)
 decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ scales,
                       const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel) {
-    const int64_t full_chunks = numel >> 4;
-    const int64_t tile_chunks = int64_t(kThreads) * kUnroll;
-    const int64_t n_tiles = (full_chunks + tile_chunks - 1) / tile_chunks;
+    // Programmatic dependent launch: let the next kernel of the stream get
+    // scheduled while this one drains, and do not touch memory before the
+    // previous kernel of the stream has completed and flushed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t c0 = tile * tile_chunks + threadIdx.x;
+    const int64_t full_chunks = numel >> 4;
+    const int64_t begin = full_chunks * blockIdx.x / gridDim.x;
+    const int64_t end = full_chunks * (blockIdx.x + 1) / gridDim.x;
+
+    for (int64_t c0 = begin + threadIdx.x; c0 < end; c0 += int64_t(kThreads) * kUnroll) {
         uint4 w[kUnroll];
         uint16_t sb[kUnroll];
         uint8_t zb[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int64_t c = c0 + int64_t(u) * kThreads;
-            if (c < full_chunks) {
+            if (c < end) {
                 w[u] = ldg_stream_v4(q + c);
                 const int64_t g = c >> LOG2_CPG;
                 sb[u] = __ldg(scales + g);
@@ -94,7 +183,7 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int64_t c = c0 + int64_t(u) * kThreads;
-            if (c < full_chunks) {
+            if (c < end) {
                 const float scale = bf16_bits_to_float(sb[u]);
                 const float zmagic = 8388608.0f + float(zb[u]);
                 uint32_t o[8];
@@ -102,11 +191,7 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
                 convert_word(w[u].y, zmagic, scale, o[2], o[3]);
                 convert_word(w[u].z, zmagic, scale, o[4], o[5]);
                 convert_word(w[u].w, zmagic, scale, o[6], o[7]);
-                uint16_t* dst = out + (c << 4);
-                if (STORE256)
-                    stg_v8(dst, o);
-                else
-                    stg_v4x2(dst, o);
+                stg_v4x2(out + (c << 4), o);
             }
         }
     }
@@ -130,14 +215,46 @@ decompress_scalar_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
     }
 }
 
-template <int LOG2_CPG>
-cudaError_t launch_vec(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel,
-                       bool store256, int grid, cudaStream_t st) {
-    if (store256)
-        decompress_vec_kernel<LOG2_CPG, true><<<grid, kThreads, 0, st>>>(reinterpret_cast<const uint4*>(q), s, zp, out, numel);
-    else
-        decompress_vec_kernel<LOG2_CPG, false><<<grid, kThreads, 0, st>>>(reinterpret_cast<const uint4*>(q), s, zp, out, numel);
-    return cudaGetLastError();
+// Blocks of `kernel` one device holds at once (occupancy x SM count), cached per device.
+template <typename K>
+int resident_blocks(K kernel, int* cache) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return tcb::sm_count() * 4;
+    if (cache[dev] == 0) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+        cache[dev] = per_sm * tcb::sm_count();
+    }
+    return cache[dev];
+}
+
+template <typename K, typename QPtr>
+cudaError_t launch_one_wave(K kernel, int* cache, int64_t units, QPtr q, const uint16_t* s, const uint8_t* zp, uint16_t* out,
+                            int64_t numel, cudaStream_t st) {
+    int64_t grid = resident_blocks(kernel, cache);
+    const int64_t min_units_per_block = kThreads;  // small inputs: fewer, fuller blocks
+    if (grid * min_units_per_block > units) grid = (units + min_units_per_block - 1) / min_units_per_block;
+    if (grid < 1) grid = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, q, s, zp, out, numel);
+}
+
+template <int LOG2_G>
+cudaError_t launch_aligned(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel,
+                           bool aligned32, cudaStream_t st) {
+    static int cache32[64] = {0}, cache16[64] = {0};
+    if (aligned32) return launch_one_wave(decompress_v8_kernel<LOG2_G>, cache32, numel >> 5, q, s, zp, out, numel, st);
+    return launch_one_wave(decompress_vec_kernel<LOG2_G - 4>, cache16, numel >> 4, reinterpret_cast<const uint4*>(q), s, zp, out,
+                           numel, st);
 }
 
 }  // namespace
@@ -158,19 +275,14 @@ int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* z
         cudaError_t e = cudaGetLastError();
         return e == cudaSuccess ? TCB_OK : cuda_fail(e, "decompress_scalar_kernel launch");
     }
-    const bool store256 = (reinterpret_cast<uintptr_t>(out) & 31) == 0;
-    const int64_t tile_chunks = int64_t(kThreads) * kUnroll;
-    int64_t n_tiles = ((numel >> 4) + tile_chunks - 1) / tile_chunks;
-    if (n_tiles < 1) n_tiles = 1;
-    const int64_t max_grid = int64_t(sms) * 8;
-    const int grid = int(n_tiles < max_grid ? n_tiles : max_grid);
+    const bool aligned32 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 31) == 0;
     cudaError_t e;
     switch (group_size) {
-    case 16: e = launch_vec<0>(q, scales, zp, out, numel, store256, grid, st); break;
-    case 32: e = launch_vec<1>(q, scales, zp, out, numel, store256, grid, st); break;
-    default: e = launch_vec<2>(q, scales, zp, out, numel, store256, grid, st); break;
+    case 16: e = launch_aligned<4>(q, scales, zp, out, numel, aligned32, st); break;
+    case 32: e = launch_aligned<5>(q, scales, zp, out, numel, aligned32, st); break;
+    default: e = launch_aligned<6>(q, scales, zp, out, numel, aligned32, st); break;
     }
-    return e == cudaSuccess ? TCB_OK : cuda_fail(e, "decompress_vec_kernel launch");
+    return e == cudaSuccess ? TCB_OK : cuda_fail(e, "decompress kernel launch");
 }
 
 }  // namespace tcb
