@@ -96,6 +96,32 @@ TCB_API int tcb_compress_amo_quality(const void* x, int dtype, int64_t numel, in
                              uint16_t* scales, uint8_t* zp, void* stream);
 
 /*
+ * Fused dequantise + GEMM on the tcgen05 tensor cores:
+ *     out[m, n] = bf16( sum_k dense[m, k] * deq(q)[n, k]  + bias )
+ * with deq(q)[n, k] = (q[n, k] - zp[n, k / G]) * scale[n, k / G]   (zp != NULL, uint8 codes)
+ *                or    int8(q[n, k])           * scale[n, k / G]   (zp == NULL, signed codes).
+ * Replaces FusedDequantLinear.forward / _fused_dequant_matmul_kernel
+ * (src/tensorcache/fused_ops.py:1338-1461).
+ *   dense  [R_d, K] bf16, K contiguous        q  [R_q, K] codes, K contiguous
+ *   scales / zp  [R_q * K / G]                out [R_d, R_q] bf16 when quant_is_rhs != 0
+ *   quant_is_rhs != 0:  out = dense . deq(q)^T   (quantised weight; bias has R_q entries)
+ *   quant_is_rhs == 0:  out[R_q, R_d] = deq(q) . dense^T  (the reference's layout: quantised
+ *                       activation, dense weight; bias has R_d entries)
+ * Requirements: K a positive multiple of 64, G in {16, 32, 64}; dense and q
+ * 16-byte aligned.  R_d and R_q are arbitrary (edge tiles are masked).
+ * Every wait inside the kernel is bounded; if one runs out the kernel records it
+ * in a per-device status word that tcb_fused_dequant_linear_check() reads.
+ */
+TCB_API int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q, const uint16_t* scales,
+                             const uint8_t* zp_or_null, const uint16_t* bias_or_null, uint16_t* out,
+                             int64_t R_d, int64_t R_q, int64_t K, int group_size, int quant_is_rhs,
+                             void* stream);
+
+/* Reads (and clears) the per-device status word the fused GEMM writes when a
+ * bounded wait runs out.  Synchronises `stream`.  Returns TCB_OK or TCB_ERR_TIMEOUT. */
+TCB_API int tcb_fused_dequant_linear_check(void* stream);
+
+/*
  * Host-side row gather used by the batch readers: copies n rows of row_bytes
  * bytes, dst[i] = src_base[idx[i]] (idx == NULL: rows first_row .. first_row+n-1,
  * i.e. one contiguous block), using up to nthreads worker threads.  Replaces

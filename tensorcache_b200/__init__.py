@@ -10,6 +10,7 @@ compute calls raise.
 """
 from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, quantize_int8_amo_bq
 from .feature_cache import FeatureCacheDataset, FeatureCacheWriter
+from .fused_linear import FusedDequantLinear, fused_dequant_matmul
 from .streamer import ZeroCopyTensorStreamer
 from .utils import compress, decompress, estimate_compression
 
@@ -17,5 +18,6 @@ __version__ = "0.1.0"
 __all__ = [
     "AMO_BQ_PRESETS", "BlockwiseInt8Codec", "quantize_int8_amo_bq", "dequantize_int8_amo_bq",
     "compress", "decompress", "estimate_compression",
+    "FusedDequantLinear", "fused_dequant_matmul",
     "FeatureCacheWriter", "FeatureCacheDataset", "ZeroCopyTensorStreamer",
 ]

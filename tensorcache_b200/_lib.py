@@ -52,6 +52,8 @@ SIGNATURES = {
     "tcb_decompress_amo": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_compress_amo": (_i32, [_vp, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tcb_compress_amo_quality": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "tcb_fused_dequant_linear": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tcb_fused_dequant_linear_check": (_i32, [_vp]),
     "tcb_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i32]),
     "tcb_streamer_create": (_i32, [ctypes.POINTER(StreamerDesc), ctypes.POINTER(_vp)]),
     "tcb_streamer_num_samples": (_i32, [_vp, ctypes.POINTER(_i64)]),

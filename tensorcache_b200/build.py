@@ -29,6 +29,7 @@ SOURCES = [
     ("decompress.cu", []),
     ("compress.cu", ["-fmad=false"]),
     ("streamer.cpp", []),
+    ("fused_linear.cu", []),
 ]
 
 

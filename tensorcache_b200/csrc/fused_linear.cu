@@ -1,0 +1,511 @@
+// Fused AMO-BQ dequantise + GEMM for sm_100a on the tcgen05 tensor cores.
+//
+//     D[r_q, r_d] = sum_k deq(q)[r_q, k] * dense[r_d, k]        (fp32 accumulation in TMEM)
+//
+// with deq(q)[r, k] = (q[r, k] - zp[r, k / G]) * scale[r, k / G].  The quantised
+// operand never exists in global memory in bf16: producer warps read the uint8
+// codes, dequantise them in registers and write bf16 straight into the shared
+// memory tile the tensor core reads (the canonical K-major, 128-byte-swizzled
+// UMMA operand layout).  The dense operand arrives by TMA into the same layout.
+//
+// One CTA per SM, persistent over output tiles of 128 (quantised rows) x 256
+// (dense rows); K advances 64 at a time through a 4-stage ring.
+//   warp 0      TMA producer: dense tile [256 x 64] bf16 per stage (one thread)
+//   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K16) per stage, commits
+//               the stage back to the producers and the finished accumulator to
+//               the epilogue (one thread); also owns the TMEM allocation
+//   warps 2-9   dequantising producers: 128 rows x 64 codes per stage
+//   warps 10-13 epilogue: tcgen05.ld -> (+bias) -> bf16 -> global
+// The 512 TMEM columns hold two 128 x 256 fp32 accumulators, so the epilogue of
+// one tile overlaps the main loop of the next.  No TMA multicast, no cluster.
+//
+// The dequantised value is bf16((q - zp) * scale): q - zp is formed exactly in
+// fp32, rounded to bf16 without error (|q - zp| <= 255 fits 8 significant bits)
+// and multiplied by the bf16 scale with one correctly rounded bf16 multiply, i.e.
+// it is the same number the decode kernel produces.
+//
+// Every wait on an mbarrier is bounded by a clock budget.  When one runs out the
+// thread raises a CTA-wide abort flag and a device status word; all roles leave
+// their loops, the CTA synchronises, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "tcb_common.h"
+
+namespace {
+
+constexpr int kTileQ = 128;      // rows of the quantised operand per tile (MMA M)
+constexpr int kTileD = 256;      // rows of the dense operand per tile (MMA N)
+constexpr int kBlockK = 64;      // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kNumProducerWarps = 8;
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 448
+constexpr int kFirstProducerWarp = 2;
+constexpr int kFirstEpilogueWarp = 2 + kNumProducerWarps;                   // 10
+constexpr uint32_t kStageBytesA = kTileQ * kBlockK * 2;                      // 16 KB
+constexpr uint32_t kStageBytesB = kTileD * kBlockK * 2;                      // 32 KB
+constexpr uint32_t kSmemTiles = kStages * (kStageBytesA + kStageBytesB);
+constexpr uint32_t kSmemBytes = kSmemTiles + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr long long kWaitBudgetClocks = 4000000000LL;  // ~2 s at 2 GHz
+
+__device__ int g_status = 0;  // 0 ok; otherwise (role << 8 | barrier id) of the first wait that ran out
+
+// ----------------------------------------------------------------------- PTX
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  Returns false if the CTA is aborting (or this wait ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitBudgetClocks) {
+            *abort_flag = 1;
+            atomicCAS(&g_status, 0, who);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+    d |= uint64_t(1) << 16;                     // leading byte offset (unused with swizzle), 16-byte units
+    d |= uint64_t(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= uint64_t(1) << 46;                     // descriptor version for sm_100
+    d |= uint64_t(2) << 61;                     // layout: 128-byte swizzle
+    return d;
+}
+
+// bf16 x bf16 -> fp32, A and B K-major, M = 128, N = 256
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileD >> 3) << 17) | (uint32_t(kTileQ >> 4) << 24);
+
+// ------------------------------------------------------------------- dequant
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// 4 code bytes -> 4 bf16 values (q - zp) * scale, packed as two bf16x2
+__device__ __forceinline__ void dequant_word(uint32_t w, float zmagic, uint32_t scale2, uint32_t& o0, uint32_t& o1) {
+    const uint32_t magic = 0x4B000000u;  // 2^23: the byte lands in the low mantissa bits
+    const float f0 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7650)), zmagic);
+    const float f1 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7651)), zmagic);
+    const float f2 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7652)), zmagic);
+    const float f3 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7653)), zmagic);
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(f0, f1);  // exact: |q - zp| <= 255
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(f2, f3);
+    o0 = bf16x2_mul(*reinterpret_cast<uint32_t*>(&p0), scale2);
+    o1 = bf16x2_mul(*reinterpret_cast<uint32_t*>(&p1), scale2);
+}
+
+struct Params {
+    const uint8_t* q;         // [R_q, K]
+    const uint16_t* scales;   // [R_q * K / G]
+    const uint8_t* zp;        // same, or null: codes are signed int8
+    const uint16_t* bias;     // null, or [R_d] (natural layout) / [R_q] (transposed output)
+    uint16_t* out;            // natural: [R_q, R_d]; transposed: [R_d, R_q]
+    int64_t R_q, R_d, K;
+    int log2_g;
+    int transpose_out;
+    int tiles_q, tiles_d;
+};
+
+// One producer thread's share of a stage: row `row` of the tile, codes [32 * half, 32 * half + 32)
+struct ProducerLoad {
+    uint4 c0, c1;          // 32 codes
+    uint32_t sbits[2];     // scale bits for codes 0-15 / 16-31 (equal unless G = 16)
+    uint32_t zvals[2];
+};
+
+__device__ __forceinline__ void producer_fetch(const Params& p, int64_t grow, int kb, int half, bool row_ok, ProducerLoad& L) {
+    if (!row_ok) {
+        L.c0 = L.c1 = make_uint4(0, 0, 0, 0);
+        L.sbits[0] = L.sbits[1] = 0;
+        L.zvals[0] = L.zvals[1] = 0;
+        return;
+    }
+    const int64_t k0 = int64_t(kb) * kBlockK + half * 32;
+    const uint4* src = reinterpret_cast<const uint4*>(p.q + grow * p.K + k0);
+    L.c0 = __ldg(src);
+    L.c1 = __ldg(src + 1);
+    const int64_t g0 = (grow * p.K + k0) >> p.log2_g;
+    const int64_t g1 = (grow * p.K + k0 + 16) >> p.log2_g;
+    L.sbits[0] = __ldg(p.scales + g0);
+    L.sbits[1] = __ldg(p.scales + g1);
+    if (p.zp) {
+        L.zvals[0] = __ldg(p.zp + g0);
+        L.zvals[1] = __ldg(p.zp + g1);
+    } else {  // signed codes: flip the sign bit and subtract 128
+        L.c0.x ^= 0x80808080u; L.c0.y ^= 0x80808080u; L.c0.z ^= 0x80808080u; L.c0.w ^= 0x80808080u;
+        L.c1.x ^= 0x80808080u; L.c1.y ^= 0x80808080u; L.c1.z ^= 0x80808080u; L.c1.w ^= 0x80808080u;
+        L.zvals[0] = L.zvals[1] = 128;
+    }
+}
+
+// Converts and writes the thread's 32 values (four 16-byte chunks) into the swizzled A tile.
+__device__ __forceinline__ void producer_store(uint8_t* a_stage, int row, int half, const ProducerLoad& L) {
+    uint8_t* row_base = a_stage + (row >> 3) * 1024 + (row & 7) * 128;
+    const int sw = row & 7;
+    const uint32_t words[8] = {L.c0.x, L.c0.y, L.c0.z, L.c0.w, L.c1.x, L.c1.y, L.c1.z, L.c1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // chunk j of this half: codes 8j .. 8j+7
+        const int h = j >> 1;
+        const float zmagic = 8388608.0f + float(L.zvals[h]);
+        const uint32_t s2 = L.sbits[h] | (L.sbits[h] << 16);
+        uint4 o;
+        dequant_word(words[2 * j], zmagic, s2, o.x, o.y);
+        dequant_word(words[2 * j + 1], zmagic, s2, o.z, o.w);
+        const int chunk = (half * 4 + j) ^ sw;
+        *reinterpret_cast<uint4*>(row_base + chunk * 16) = o;
+    }
+}
+
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
+    __nv_bfloat16 b = __float2bfloat16_rn(v);
+    return *reinterpret_cast<uint16_t*>(&b);
+}
+
+// -------------------------------------------------------------------- kernel
+
+__global__ void __launch_bounds__(kThreads, 1)
+fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;                                   // kStages x 16 KB, dequantised operand
+    uint8_t* smem_b = smem + kStages * kStageBytesA;          // kStages x 32 KB, dense operand (TMA)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
+    // barrier ids: [0,S) full_b, [S,2S) full_a, [2S,3S) empty, 3S+{0,1} tmem_full, 3S+{2,3} tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int id) { return bar0 + 8u * uint32_t(id); };
+    const int FULL_B = 0, FULL_A = kStages, EMPTY = 2 * kStages, TFULL = 3 * kStages, TEMPTY = 3 * kStages + 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(FULL_B + s), 1);
+            mbar_init(bar(FULL_A + s), kNumProducerWarps * 32);
+            mbar_init(bar(EMPTY + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(TFULL + b), 1);
+            mbar_init(bar(TEMPTY + b), kNumEpilogueWarps * 32);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_kb = int(p.K / kBlockK);
+    const int num_tiles = p.tiles_q * p.tiles_d;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (dense operand)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int td = tile % p.tiles_d;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, (1 << 8) | (EMPTY + s)))) break;
+                    mbar_arrive_expect_tx(bar(FULL_B + s), kStageBytesB);
+                    tma_load_2d(smem_u32(smem_b + s * kStageBytesB), &dense_map, kb * kBlockK, td * kTileD, bar(FULL_B + s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+                const int buf = local_tile & 1;
+                const uint32_t tph = (local_tile >> 1) & 1;
+                if (!(ok = mbar_wait(bar(TEMPTY + buf), tph ^ 1, abort_flag, (2 << 8) | (TEMPTY + buf)))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(buf * kTileD);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1;
+                    if (!(ok = mbar_wait(bar(FULL_B + s), ph, abort_flag, (2 << 8) | (FULL_B + s)))) break;
+                    if (!(ok = mbar_wait(bar(FULL_A + s), ph, abort_flag, (2 << 8) | (FULL_A + s)))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesA);
+                    const uint32_t b_addr = smem_u32(smem_b + s * kStageBytesB);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k)
+                        umma_bf16(d_tmem, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), kInstrDesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar(EMPTY + s));  // the stage may be refilled once these MMAs have read it
+                }
+                if (ok) umma_commit(bar(TFULL + buf));  // accumulator complete
+            }
+        }
+    } else if (warp < kFirstEpilogueWarp) {
+        // ------------------------------------------------ dequantising producers
+        const int pt = threadIdx.x - kFirstProducerWarp * 32;  // 0..255
+        const int row = pt >> 1, half = pt & 1;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const int tq = tile / p.tiles_d;
+            const int64_t grow = int64_t(tq) * kTileQ + row;
+            const bool row_ok = grow < p.R_q;
+            ProducerLoad cur, nxt;
+            producer_fetch(p, grow, 0, half, row_ok, cur);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if (kb + 1 < num_kb) producer_fetch(p, grow, kb + 1, half, row_ok, nxt);
+                const int s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1;
+                if (!(ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, (3 << 8) | (EMPTY + s)))) break;
+                producer_store(smem_a + s * kStageBytesA, row, half, cur);
+                fence_proxy_async();  // make the generic-proxy stores visible to the tensor core
+                mbar_arrive(bar(FULL_A + s));
+                cur = nxt;
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue
+        const int ew = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int r_in_tile = ew * 32 + lane;    // accumulator row = quantised-operand row
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const int tq = tile / p.tiles_d, td = tile % p.tiles_d;
+            const int buf = local_tile & 1;
+            const uint32_t tph = (local_tile >> 1) & 1;
+            if (!(ok = mbar_wait(bar(TFULL + buf), tph, abort_flag, (4 << 8) | (TFULL + buf)))) break;
+            tc_fence_after();
+            const int64_t rq = int64_t(tq) * kTileQ + r_in_tile;
+            const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(buf * kTileD);
+            float bias_row = 0.0f;
+            if (p.bias && p.transpose_out && rq < p.R_q) bias_row = __uint_as_float(uint32_t(p.bias[rq]) << 16);
+#pragma unroll 1
+            for (int c = 0; c < kTileD / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(taddr0 + uint32_t(c * 32), v);
+                tmem_ld_wait();
+                const int64_t rd0 = int64_t(td) * kTileD + c * 32;
+                if (p.transpose_out) {
+                    // out[r_d, r_q]: for a fixed register the 32 lanes write 32 consecutive r_q
+                    if (rq < p.R_q) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (rd0 + i < p.R_d) p.out[(rd0 + i) * p.R_q + rq] = f32_to_bf16_bits(__uint_as_float(v[i]) + bias_row);
+                    }
+                } else if (rq < p.R_q) {
+                    // out[r_q, r_d]: each lane owns 32 consecutive r_d of its row
+                    uint16_t* dst = p.out + rq * p.R_d + rd0;
+                    if (rd0 + 32 <= p.R_d && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
+                            if (p.bias) {
+                                a += __uint_as_float(uint32_t(p.bias[rd0 + 2 * i]) << 16);
+                                b += __uint_as_float(uint32_t(p.bias[rd0 + 2 * i + 1]) << 16);
+                            }
+                            w[i] = uint32_t(f32_to_bf16_bits(a)) | (uint32_t(f32_to_bf16_bits(b)) << 16);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (rd0 + i < p.R_d) {
+                                float a = __uint_as_float(v[i]);
+                                if (p.bias) a += __uint_as_float(uint32_t(p.bias[rd0 + i]) << 16);
+                                dst[i] = f32_to_bf16_bits(a);
+                            }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(TEMPTY + buf));  // this accumulator may be overwritten
+        }
+    }
+
+    // common exit: normal completion or abort
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// -------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+}  // namespace
+
+extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q, const uint16_t* scales, const uint8_t* zp_or_null,
+                                        const uint16_t* bias_or_null, uint16_t* out, int64_t R_d, int64_t R_q, int64_t K,
+                                        int group_size, int quant_is_rhs, void* stream) {
+    const char* who = "tcb_fused_dequant_linear";
+    if (R_d < 0 || R_q < 0 || K < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: negative size", who);
+    if (!tcb::group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+    if (R_d == 0 || R_q == 0) return TCB_OK;
+    if (K == 0 || K % kBlockK != 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: K = %lld must be a positive multiple of %d", who, (long long)K, kBlockK);
+    if (!dense || !q || !scales || !out) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);
+    if ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(q)) & 15)
+        return tcb::fail(TCB_ERR_ALIGNMENT, "%s: dense and q must be 16-byte aligned", who);
+    if ((reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias_or_null)) & 1)
+        return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales, bias and out must be 2-byte aligned", who);
+    if (R_d > (int64_t(1) << 31) - 1 || R_q > (int64_t(1) << 31) - 1 || K > (int64_t(1) << 31) - 1)
+        return tcb::fail(TCB_ERR_TOO_LARGE, "%s: dimension beyond 2^31 - 1", who);
+    const int64_t tiles_q = (R_q + kTileQ - 1) / kTileQ, tiles_d = (R_d + kTileD - 1) / kTileD;
+    if (tiles_q * tiles_d > (int64_t(1) << 30)) return tcb::fail(TCB_ERR_TOO_LARGE, "%s: too many output tiles", who);
+
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(R_d)};
+    const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileD)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(dense), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", who, int(cr));
+
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    TCB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        TCB_CUDA_TRY(cudaFuncSetAttribute(fused_dequant_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+        attr_set[dev] = true;
+    }
+    Params p;
+    p.q = q;
+    p.scales = scales;
+    p.zp = zp_or_null;
+    p.bias = bias_or_null;
+    p.out = out;
+    p.R_q = R_q;
+    p.R_d = R_d;
+    p.K = K;
+    p.log2_g = group_size == 16 ? 4 : group_size == 32 ? 5 : 6;
+    p.transpose_out = quant_is_rhs ? 1 : 0;
+    p.tiles_q = int(tiles_q);
+    p.tiles_d = int(tiles_d);
+    const int64_t num_tiles = tiles_q * tiles_d;
+    const int sms = tcb::sm_count();
+    const int grid = int(num_tiles < sms ? num_tiles : sms);
+    fused_dequant_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
+}
+
+extern "C" int tcb_fused_dequant_linear_check(void* stream) {
+    TCB_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int status = 0;
+    TCB_CUDA_TRY(cudaMemcpyFromSymbol(&status, g_status, sizeof(int)));
+    if (status == 0) return TCB_OK;
+    const int zero = 0;
+    TCB_CUDA_TRY(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+    return tcb::fail(TCB_ERR_TIMEOUT, "tcb_fused_dequant_linear: a bounded wait ran out (role %d, barrier %d)", status >> 8, status & 0xff);
+}

@@ -18,7 +18,7 @@ def declared_symbols():
 
 def test_header_declares_the_expected_surface():
     names = declared_symbols()
-    for must in ("tcb_decompress_amo", "tcb_compress_amo", "tcb_compress_amo_quality", "tcb_gather_rows",
+    for must in ("tcb_decompress_amo", "tcb_compress_amo", "tcb_compress_amo_quality", "tcb_fused_dequant_linear", "tcb_gather_rows",
                  "tcb_streamer_create", "tcb_streamer_next", "tcb_last_error", "tcb_version"):
         assert must in names
 
@@ -48,6 +48,8 @@ def test_argument_validation_happens_before_any_device_work(built_lib):
     assert L.tcb_compress_amo(None, 7, 10, 32, m, 4, None, None, None, None) == _lib.ERR_BAD_ARG  # dtype
     assert L.tcb_compress_amo_quality(None, 0, 10, 48, None, None, None, None) == _lib.ERR_GROUP_SIZE
     assert L.tcb_compress_amo_quality(None, 0, 0, 16, None, None, None, None) == _lib.TCB_OK
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 100, 32, 1, None) == _lib.ERR_BAD_ARG  # K % 64
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 128, 32, 1, None) == _lib.ERR_BAD_ARG  # nulls
     with pytest.raises(ValueError):
         _lib.check(_lib.ERR_GROUP_SIZE)
 

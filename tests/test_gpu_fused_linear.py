@@ -1,0 +1,131 @@
+"""FusedDequantLinear (tcgen05 GEMM with in-kernel dequantisation) against an fp32
+dequantise-then-matmul.  Tolerance: relative Frobenius error <= 1e-2 (the bar the
+benchmark states); the expected error of a bf16 operand + bf16 output is ~2.5e-3,
+so the tests also assert a tighter 5e-3 to catch a half-broken tile."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import tensorcache_b200 as tc
+from tensorcache_b200.fused_linear import check_device_status
+from tests import synth
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 1e-2
+EXPECTED = 5e-3
+
+
+def dequant_f32(codes, scales, zp, G):
+    R, K = codes.shape
+    c = codes.float().view(R, K // G, G)
+    if zp is not None:
+        c = c - zp.float().view(R, K // G, 1)
+    return (c * scales.float().view(R, K // G, 1)).view(R, K)
+
+
+def rel_fro(got, ref):
+    return ((got.float() - ref).norm() / ref.norm()).item()
+
+
+@pytest.mark.parametrize("M,N,K,G", [(256, 128, 64, 32), (128, 512, 768, 32), (300, 200, 256, 16), (77, 1000, 1024, 64),
+                                     (1, 1, 64, 32), (2048, 1536, 2048, 32)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_quantised_weight_matmul(M, N, K, G, with_bias):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV) if with_bias else None
+    wq, ws, wzp, _ = tc.compress(w, "balanced", G)
+    y = tc.fused_dequant_matmul(x, wq.view(N, K), ws, wzp, bias, G)
+    check_device_status()
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    ref = x.float() @ dequant_f32(wq.view(N, K), ws, wzp, G).T
+    if bias is not None:
+        ref = ref + bias.float()
+    err = rel_fro(y, ref)
+    assert err <= TOL and err <= EXPECTED, err
+    # every element individually: bf16 output rounding plus accumulation-order noise
+    assert bool(((y.float() - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-3 * ref.abs().max()).all())
+
+
+def test_reference_module_semantics_signed_activation():
+    """tests/test_fused_ops.py:254-280 of the reference: M,K,N = 128,768,512, symmetric int8
+    activation codes, dense bf16 weight, bias; leading dimensions preserved."""
+    torch.manual_seed(0)
+    M, K, N, G = 128, 768, 512, 32
+    layer = tc.FusedDequantLinear(K, N, bias=True, group_size=G).to(DEV)
+    assert layer.weight.dtype == torch.bfloat16 and layer.weight.shape == (N, K) and layer.bias.shape == (N,)
+    with torch.no_grad():
+        layer.bias.copy_(torch.randn(N))
+    a = torch.randn(4, M // 4, K, device=DEV)
+    blocks = a.view(-1, G)
+    s = (blocks.abs().amax(1) / 127.0).clamp(min=1e-8).to(torch.bfloat16)
+    q = torch.clamp(torch.round(blocks / s.float().view(-1, 1)), -127, 127).to(torch.int8).view(4, M // 4, K)
+    y = layer(q, s)
+    check_device_status()
+    assert y.shape == (4, M // 4, N)
+    ref = dequant_f32(q.view(M, K), s, None, G) @ layer.weight.float().T + layer.bias.float()
+    err = rel_fro(y.view(M, N), ref)
+    assert err <= 0.005, err   # the reference's own test bound is 0.5 %
+
+
+def test_module_with_amo_activation_codes():
+    M, K, N, G = 200, 512, 384, 16
+    layer = tc.FusedDequantLinear(K, N, bias=False, group_size=G).to(DEV)
+    a = synth.config0_style(9, (M, K)).to(DEV)
+    q, s, zp, _ = tc.compress(a, "quality", G)
+    y = layer(q.view(M, K), s, zp)
+    check_device_status()
+    ref = dequant_f32(q.view(M, K), s, zp, G) @ layer.weight.float().T
+    assert rel_fro(y, ref) <= EXPECTED
+
+
+def test_dequantised_operand_equals_the_decode_kernel_bits():
+    """With an identity dense operand the GEMM returns the dequantised operand itself:
+    it must be bit-identical with tc.decompress (same arithmetic, exact accumulation)."""
+    K, R, G = 128, 256, 32
+    w = synth.config0_style(12, (R, K)).to(DEV)
+    wq, ws, wzp, _ = tc.compress(w, "balanced", G)
+    eye = torch.eye(K, dtype=torch.bfloat16, device=DEV)
+    y = tc.fused_dequant_matmul(eye, wq.view(R, K), ws, wzp, None, G)      # [K, R] = deq(W)^T
+    check_device_status()
+    want = tc.decompress(wq, ws, (R, K), wzp, G)
+    assert torch.equal(y.t().contiguous().view(torch.int16), want.view(torch.int16))
+
+
+def test_argument_errors():
+    x = torch.zeros(8, 96, dtype=torch.bfloat16, device=DEV)
+    wq = torch.zeros(8, 96, dtype=torch.uint8, device=DEV)
+    with pytest.raises(ValueError, match="multiple of 64"):
+        tc.fused_dequant_matmul(x, wq, torch.zeros(24, dtype=torch.bfloat16, device=DEV), torch.zeros(24, dtype=torch.uint8, device=DEV))
+    wq = torch.zeros(8, 128, dtype=torch.uint8, device=DEV)
+    with pytest.raises(ValueError):
+        tc.fused_dequant_matmul(torch.zeros(8, 128, dtype=torch.bfloat16, device=DEV), wq,
+                                torch.zeros(3, dtype=torch.bfloat16, device=DEV), torch.zeros(32, dtype=torch.uint8, device=DEV))
+    from tensorcache_b200 import _lib
+    L = _lib.lib()
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 100, 32, 1, None) == _lib.ERR_BAD_ARG
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 128, 48, 1, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 0, 8, 128, 32, 1, None) == _lib.TCB_OK
+
+
+def test_benchmark_shape_tolerance():
+    """X [8192,4096] ~ N(0,1), W [14336,4096] ~ N(0, std 0.02) AMO-BQ balanced G32 along K."""
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    w = (0.02 * torch.randn((14336, 4096), generator=gen, device=DEV)).to(torch.bfloat16)
+    x = torch.randn((8192, 4096), generator=gen, device=DEV).to(torch.bfloat16)
+    wq, ws, wzp, _ = tc.compress(w, "balanced", 32)
+    y = tc.fused_dequant_matmul(x, wq.view(14336, 4096), ws, wzp, None, 32)
+    check_device_status()
+    wd = dequant_f32(wq.view(14336, 4096), ws, wzp, 32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    num = den = 0.0
+    for r0 in range(0, 8192, 1024):   # fp32 reference in row blocks
+        ref = x[r0:r0 + 1024].float() @ wd.T
+        num += float(((y[r0:r0 + 1024].float() - ref) ** 2).sum())
+        den += float((ref ** 2).sum())
+    err = (num / den) ** 0.5
+    assert err <= TOL and err <= EXPECTED, err
