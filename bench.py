@@ -265,6 +265,86 @@ def time_streamer(tc, prefix, device, steps, warmup, shuffle, barrier):
     return secs, h2d, token.numel() * 2
 
 
+def tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            j = json.loads(p.read_text())
+            return float(j["bf16_tflops_sustained"]), float(j["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1400.0, 1590.0, "fallback"
+
+
+def run_other_workload(args):
+    """Single-GPU timings of the other kernels of the path (not the headline line):
+    fused_linear: X [8192,4096] bf16 x AMO-BQ balanced G32 weight [14336,4096]  -> TFLOP/s
+    compress:     bf16 [256,1024,1024] Student-t(4) x lognormal channel scale   -> Gvalues/s"""
+    import tensorcache_b200 as tc
+    from tensorcache_b200.fused_linear import check_device_status
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.workload == "fused_linear":
+        M, N, K = (int(v) for v in args.shape.split(",")) if args.shape else (8192, 14336, 4096)
+        w = (0.02 * torch.randn((N, K), generator=gen, device=device)).to(torch.bfloat16)
+        x = torch.randn((M, K), generator=gen, device=device).to(torch.bfloat16)
+        wq, ws, wzp, _ = tc.compress(w, "balanced", args.group_size)
+        wq = wq.view(N, K)
+        del w
+        fn = lambda: tc.fused_dequant_matmul(x, wq, ws, wzp, None, args.group_size)
+        work, unit, metric = 2.0 * M * N * K / 1e12, "TFLOP/s", "fused_dequant_linear_throughput"
+        cfg = {"workload": f"FusedDequantLinear X[{M},{K}] bf16 x AMO-BQ balanced G{args.group_size} W[{N},{K}] -> bf16 [{M},{N}]"}
+    else:
+        B, R, C = (int(v) for v in args.shape.split(",")) if args.shape else (256, 1024, 1024)
+        ch = torch.exp(torch.randn(C, generator=gen, device=device))
+        x = torch.empty((B, R, C), dtype=torch.bfloat16, device=device)
+        for b in range(0, B, 32):
+            n = min(32, B - b)
+            z = torch.randn((n, R, C), generator=gen, device=device)
+            wv = torch.randn((4, n, R, C), generator=gen, device=device)
+            x[b:b + n] = (z / torch.sqrt((wv * wv).sum(0) / 4) * ch).to(torch.bfloat16)
+            del z, wv
+        fn = lambda: tc.compress(x, args.mode, args.group_size)
+        work, unit, metric = x.numel() / 1e9, "Gvalues/s", f"amo_bq_compress_{args.mode}_g{args.group_size}_throughput"
+        cfg = {"workload": f"AMO-BQ compress mode={args.mode} G{args.group_size} of bf16 [{B},{R},{C}]",
+               "algorithmic_bytes_per_value": 3.0 + 3.0 / args.group_size}
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    ev0.record()
+    for _ in range(args.steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize(device)
+    clocks = sampler.stop()
+    if args.workload == "fused_linear":
+        check_device_status()
+    secs = ev0.elapsed_time(ev1) / 1e3
+    value = work * args.steps / secs
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "data": "synthetic", "config": cfg,
+            "gpu_launches": args.steps, "clocks": clocks}
+    if args.workload == "fused_linear":
+        sustained, burst, kind = tensor_peak()
+        line["dtype"] = "bf16 operands (dequantised in-kernel), fp32 accumulate"
+        line["roofline"] = {"bound": "tensor", "achieved": value, "peak": sustained, "unit": "TFLOP/s", "frac": value / sustained,
+                            "frac_of_burst": value / burst, "peak_kind": kind, "traffic": None}
+    else:
+        hbm, kind = peaks()
+        gbs = value * (3.0 + 3.0 / args.group_size)
+        line["dtype"] = "fp32 (IEEE div / rint, no FMA)"
+        line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_kind": kind,
+                            "traffic": None, "note": "the encoder is ALU-bound (one IEEE division and ~10 dependent fp32 operations "
+                            "per value and candidate); the HBM fraction is low by construction"}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -274,10 +354,17 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="batches timed through the streamer (default: min(steps, 200))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="skip the streamer / e2e leg (for profiler captures)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "fused_linear", "compress"],
+                    help="decode (default) is the headline metric; the other two time the remaining kernels of the path")
+    ap.add_argument("--shape", default="", help="fused_linear: M,N,K; compress: B,R,C (defaults: the benchmark configurations)")
+    ap.add_argument("--mode", default="balanced", help="compress: AMO-BQ mode")
+    ap.add_argument("--group-size", type=int, default=G)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.workload != "decode":
+        return run_other_workload(args)
 
     import torch.distributed as dist
 

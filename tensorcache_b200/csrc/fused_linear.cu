@@ -9,12 +9,18 @@
 // UMMA operand layout).  The dense operand arrives by TMA into the same layout.
 //
 // One CTA per SM, persistent over output tiles of 128 (quantised rows) x 256
-// (dense rows); K advances 64 at a time through a 4-stage ring.
-//   warp 0      TMA producer: dense tile [256 x 64] bf16 per stage (one thread)
+// (dense rows); K advances 64 at a time through a 3-stage ring.
+//   warp 0      TMA producer: dense tile [256 x 64] bf16 and raw code tile [128 x 64]
+//               uint8 per stage (one thread)
 //   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K16) per stage, commits
 //               the stage back to the producers and the finished accumulator to
 //               the epilogue (one thread); also owns the TMEM allocation
-//   warps 2-9   dequantising producers: 128 rows x 64 codes per stage
+//   warps 2-9   dequantising producers: read the raw codes from shared memory,
+//               write 128 rows x 64 bf16 per stage; scales / zero points come from a
+//               double-buffered shared-memory chunk (32 groups per row) that the
+//               producers refill themselves one chunk ahead.  (Fetching codes and
+//               scales with per-thread global loads instead capped the kernel at
+//               ~740 TFLOP/s: the LSU miss path, not the math, was the limit.)
 //   warps 10-13 epilogue: tcgen05.ld -> (+bias) -> bf16 -> global
 // The 512 TMEM columns hold two 128 x 256 fp32 accumulators, so the epilogue of
 // one tile overlaps the main loop of the next.  No TMA multicast, no cluster.
@@ -37,7 +43,7 @@ namespace {
 constexpr int kTileQ = 128;      // rows of the quantised operand per tile (MMA M)
 constexpr int kTileD = 256;      // rows of the dense operand per tile (MMA N)
 constexpr int kBlockK = 64;      // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kNumProducerWarps = 8;
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 448
@@ -45,7 +51,11 @@ constexpr int kFirstProducerWarp = 2;
 constexpr int kFirstEpilogueWarp = 2 + kNumProducerWarps;                   // 10
 constexpr uint32_t kStageBytesA = kTileQ * kBlockK * 2;                      // 16 KB
 constexpr uint32_t kStageBytesB = kTileD * kBlockK * 2;                      // 32 KB
-constexpr uint32_t kSmemTiles = kStages * (kStageBytesA + kStageBytesB);
+constexpr uint32_t kStageBytesC = kTileQ * kBlockK;                          // 8 KB of raw codes
+constexpr int kChunkGroups = 32;                                             // groups per row per scale chunk
+constexpr uint32_t kChunkBytesS = kTileQ * kChunkGroups * 2;                 // 8 KB of bf16 scales
+constexpr uint32_t kChunkBytesZ = kTileQ * kChunkGroups;                     // 4 KB of zero points
+constexpr uint32_t kSmemTiles = kStages * (kStageBytesA + kStageBytesB + kStageBytesC) + 2 * (kChunkBytesS + kChunkBytesZ);
 constexpr uint32_t kSmemBytes = kSmemTiles + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr long long kWaitBudgetClocks = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -167,10 +177,12 @@ __device__ __forceinline__ void dequant_word(uint32_t w, float zmagic, uint32_t 
     const float f1 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7651)), zmagic);
     const float f2 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7652)), zmagic);
     const float f3 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7653)), zmagic);
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(f0, f1);  // exact: |q - zp| <= 255
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(f2, f3);
-    o0 = bf16x2_mul(*reinterpret_cast<uint32_t*>(&p0), scale2);
-    o1 = bf16x2_mul(*reinterpret_cast<uint32_t*>(&p1), scale2);
+    // |q - zp| <= 255 has at most 8 significant bits, so the upper half of the fp32
+    // pattern IS the bf16 value: pack by byte permute, no conversion instruction
+    const uint32_t p0 = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+    const uint32_t p1 = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    o0 = bf16x2_mul(p0, scale2);
+    o1 = bf16x2_mul(p1, scale2);
 }
 
 struct Params {
@@ -180,53 +192,87 @@ struct Params {
     const uint16_t* bias;     // null, or [R_d] (natural layout) / [R_q] (transposed output)
     uint16_t* out;            // natural: [R_q, R_d]; transposed: [R_d, R_q]
     int64_t R_q, R_d, K;
+    int64_t gpr;              // groups per row = K / G
+    int chunk_vec_ok;         // scales / zero points of a chunk can be fetched with 16-byte loads
     int log2_g;
     int transpose_out;
     int tiles_q, tiles_d;
 };
 
-// One producer thread's share of a stage: row `row` of the tile, codes [32 * half, 32 * half + 32)
-struct ProducerLoad {
-    uint4 c0, c1;          // 32 codes
-    uint32_t sbits[2];     // scale bits for codes 0-15 / 16-31 (equal unless G = 16)
-    uint32_t zvals[2];
+// Scales and zero points reach the producers through a small shared-memory
+// buffer that covers 32 groups per row ("a chunk": 512 / 1024 / 2048 values of K for
+// G = 16 / 32 / 64).  Thread (row, half) of the 256 producers fetches groups
+// [16 * half, 16 * half + 16) of its row into registers one chunk ahead and spills
+// them into the other half of the double buffer when the chunk turns over.  Per
+// stage the producers then need only two shared-memory reads instead of two
+// sector-wasting global loads, which keeps the LSU miss path almost idle.
+struct ChunkRegs {
+    uint4 s0, s1;  // 16 bf16 scales
+    uint4 z;       // 16 zero points
 };
 
-__device__ __forceinline__ void producer_fetch(const Params& p, int64_t grow, int kb, int half, bool row_ok, ProducerLoad& L) {
-    if (!row_ok) {
-        L.c0 = L.c1 = make_uint4(0, 0, 0, 0);
-        L.sbits[0] = L.sbits[1] = 0;
-        L.zvals[0] = L.zvals[1] = 0;
+__device__ __forceinline__ void chunk_fetch(const Params& p, int64_t grow, int64_t g_first, bool row_ok, ChunkRegs& c) {
+    c.s0 = c.s1 = c.z = make_uint4(0, 0, 0, 0);
+    if (!row_ok || g_first >= p.gpr) return;
+    const int64_t base = grow * p.gpr + g_first;
+    if (p.chunk_vec_ok && g_first + 16 <= p.gpr) {
+        const uint4* sp = reinterpret_cast<const uint4*>(p.scales + base);
+        c.s0 = __ldg(sp);
+        c.s1 = __ldg(sp + 1);
+        if (p.zp) c.z = __ldg(reinterpret_cast<const uint4*>(p.zp + base));
         return;
     }
-    const int64_t k0 = int64_t(kb) * kBlockK + half * 32;
-    const uint4* src = reinterpret_cast<const uint4*>(p.q + grow * p.K + k0);
-    L.c0 = __ldg(src);
-    L.c1 = __ldg(src + 1);
-    const int64_t g0 = (grow * p.K + k0) >> p.log2_g;
-    const int64_t g1 = (grow * p.K + k0 + 16) >> p.log2_g;
-    L.sbits[0] = __ldg(p.scales + g0);
-    L.sbits[1] = __ldg(p.scales + g1);
-    if (p.zp) {
-        L.zvals[0] = __ldg(p.zp + g0);
-        L.zvals[1] = __ldg(p.zp + g1);
-    } else {  // signed codes: flip the sign bit and subtract 128
-        L.c0.x ^= 0x80808080u; L.c0.y ^= 0x80808080u; L.c0.z ^= 0x80808080u; L.c0.w ^= 0x80808080u;
-        L.c1.x ^= 0x80808080u; L.c1.y ^= 0x80808080u; L.c1.z ^= 0x80808080u; L.c1.w ^= 0x80808080u;
-        L.zvals[0] = L.zvals[1] = 128;
-    }
+    uint32_t sw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, zw[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int e = 0; e < 16; ++e)
+        if (g_first + e < p.gpr) {
+            sw[e >> 1] |= uint32_t(__ldg(p.scales + base + e)) << (16 * (e & 1));
+            if (p.zp) zw[e >> 2] |= uint32_t(__ldg(p.zp + base + e)) << (8 * (e & 3));
+        }
+    c.s0 = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+    c.s1 = make_uint4(sw[4], sw[5], sw[6], sw[7]);
+    c.z = make_uint4(zw[0], zw[1], zw[2], zw[3]);
 }
 
-// Converts and writes the thread's 32 values (four 16-byte chunks) into the swizzled A tile.
-__device__ __forceinline__ void producer_store(uint8_t* a_stage, int row, int half, const ProducerLoad& L) {
+__device__ __forceinline__ void chunk_spill(uint8_t* sbuf, uint8_t* zbuf, int row, int half, const ChunkRegs& c) {
+    uint4* sd = reinterpret_cast<uint4*>(sbuf + row * (kChunkGroups * 2) + half * 32);
+    sd[0] = c.s0;
+    sd[1] = c.s1;
+    *reinterpret_cast<uint4*>(zbuf + row * kChunkGroups + half * 16) = c.z;
+}
+
+// One producer thread's share of a stage: row `row` of the tile, codes [32 * half, 32 * half + 32).
+// Reads the raw codes the TMA delivered (rows of 64 bytes), dequantises them and writes four
+// 16-byte chunks of bf16 into the 128-byte-swizzled A tile.  `gi` is the index, inside the
+// current scale chunk, of the group that holds the thread's first code.
+__device__ __forceinline__ void producer_convert(const uint8_t* c_stage, uint8_t* a_stage, const uint8_t* sbuf, const uint8_t* zbuf,
+                                                 int row, int half, int gi, bool two_groups, bool has_zp) {
+    // the two 16-byte reads of a thread are ordered so that a quarter warp touches 8 distinct bank groups
+    const int flip = (row >> 1) & 1;
+    const uint4* crow = reinterpret_cast<const uint4*>(c_stage + row * kBlockK + half * 32);
+    const uint4 ca = crow[flip], cb = crow[flip ^ 1];
+    const uint4 c0 = flip ? cb : ca, c1 = flip ? ca : cb;
+    uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const uint16_t* srow = reinterpret_cast<const uint16_t*>(sbuf + row * (kChunkGroups * 2));
+    const uint8_t* zrow = zbuf + row * kChunkGroups;
+    uint32_t sb[2], zv[2];
+    sb[0] = srow[gi];
+    sb[1] = two_groups ? uint32_t(srow[gi + 1]) : sb[0];
+    if (has_zp) {
+        zv[0] = zrow[gi];
+        zv[1] = two_groups ? uint32_t(zrow[gi + 1]) : zv[0];
+    } else {  // signed codes: flip the sign bit and subtract 128
+#pragma unroll
+        for (int i = 0; i < 8; ++i) words[i] ^= 0x80808080u;
+        zv[0] = zv[1] = 128;
+    }
     uint8_t* row_base = a_stage + (row >> 3) * 1024 + (row & 7) * 128;
     const int sw = row & 7;
-    const uint32_t words[8] = {L.c0.x, L.c0.y, L.c0.z, L.c0.w, L.c1.x, L.c1.y, L.c1.z, L.c1.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {  // chunk j of this half: codes 8j .. 8j+7
         const int h = j >> 1;
-        const float zmagic = 8388608.0f + float(L.zvals[h]);
-        const uint32_t s2 = L.sbits[h] | (L.sbits[h] << 16);
+        const float zmagic = __uint_as_float(0x4B000000u | zv[h]);  // 2^23 + zp, exact
+        const uint32_t s2 = sb[h] | (sb[h] << 16);
         uint4 o;
         dequant_word(words[2 * j], zmagic, s2, o.x, o.y);
         dequant_word(words[2 * j + 1], zmagic, s2, o.z, o.w);
@@ -243,32 +289,39 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
 // -------------------------------------------------------------------- kernel
 
 __global__ void __launch_bounds__(kThreads, 1)
-fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const Params p) {
+fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const __grid_constant__ CUtensorMap code_map, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;                                   // kStages x 16 KB, dequantised operand
     uint8_t* smem_b = smem + kStages * kStageBytesA;          // kStages x 32 KB, dense operand (TMA)
+    uint8_t* smem_c = smem_b + kStages * kStageBytesB;        // kStages x 8 KB, raw codes (TMA)
+    uint8_t* smem_s = smem_c + kStages * kStageBytesC;        // 2 x 8 KB, scales of the current / next chunk
+    uint8_t* smem_z = smem_s + 2 * kChunkBytesS;              // 2 x 4 KB, zero points
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
-    // barrier ids: [0,S) full_b, [S,2S) full_a, [2S,3S) empty, 3S+{0,1} tmem_full, 3S+{2,3} tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
+    // barrier ids: [0,S) full_b, [S,2S) full_a, [2S,3S) empty, [3S,4S) full_c, 4S+{0,1} tmem_full, 4S+{2,3} tmem_empty,
+    // 4S+4 chunk turn-over among the producers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int id) { return bar0 + 8u * uint32_t(id); };
-    const int FULL_B = 0, FULL_A = kStages, EMPTY = 2 * kStages, TFULL = 3 * kStages, TEMPTY = 3 * kStages + 2;
+    const int FULL_B = 0, FULL_A = kStages, EMPTY = 2 * kStages, FULL_C = 3 * kStages, TFULL = 4 * kStages, TEMPTY = 4 * kStages + 2,
+              CHUNK = 4 * kStages + 4;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(FULL_B + s), 1);
             mbar_init(bar(FULL_A + s), kNumProducerWarps * 32);
             mbar_init(bar(EMPTY + s), 1);
+            mbar_init(bar(FULL_C + s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(TFULL + b), 1);
             mbar_init(bar(TEMPTY + b), kNumEpilogueWarps * 32);
         }
+        mbar_init(bar(CHUNK), kNumProducerWarps * 32);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -285,16 +338,18 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const P
     const int num_tiles = p.tiles_q * p.tiles_d;
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer (dense operand)
+        // ------------------------------------------------ TMA producer (dense operand and raw codes)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int td = tile % p.tiles_d;
+                const int td = tile % p.tiles_d, tq = tile / p.tiles_d;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
                     if (!(ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, (1 << 8) | (EMPTY + s)))) break;
+                    mbar_arrive_expect_tx(bar(FULL_C + s), kStageBytesC);
+                    tma_load_2d(smem_u32(smem_c + s * kStageBytesC), &code_map, kb * kBlockK, tq * kTileQ, bar(FULL_C + s));
                     mbar_arrive_expect_tx(bar(FULL_B + s), kStageBytesB);
                     tma_load_2d(smem_u32(smem_b + s * kStageBytesB), &dense_map, kb * kBlockK, td * kTileD, bar(FULL_B + s));
                 }
@@ -330,25 +385,55 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const P
         }
     } else if (warp < kFirstEpilogueWarp) {
         // ------------------------------------------------ dequantising producers
+        // Per stage: wait for the raw codes (which the TMA thread only requests once the
+        // stage's previous MMAs have released it), convert, publish.  Scales and zero
+        // points come from the chunk buffer; the registers for the next chunk are
+        // fetched one chunk ahead, across tile boundaries too.
         const int pt = threadIdx.x - kFirstProducerWarp * 32;  // 0..255
         const int row = pt >> 1, half = pt & 1;
-        uint32_t it = 0;
+        const bool has_zp = p.zp != nullptr;
+        const bool two_groups = p.log2_g == 4;
+        const int log2_cs = p.log2_g - 1;                      // stages per chunk = 32 * G / 64
+        const int cs_mask = (1 << log2_cs) - 1;
+        const int chunks_per_tile = (num_kb + cs_mask) >> log2_cs;
+        // cursor of the chunk prefetch: (tile, chunk inside the tile)
+        int pf_tile = blockIdx.x, pf_chunk = 0;
+        ChunkRegs regs;
+        auto fetch_next_chunk = [&]() {
+            if (pf_tile < num_tiles) {
+                const int64_t grow = int64_t(pf_tile / p.tiles_d) * kTileQ + row;
+                chunk_fetch(p, grow, int64_t(pf_chunk) * kChunkGroups + half * 16, grow < p.R_q, regs);
+            }
+            if (++pf_chunk == chunks_per_tile) {
+                pf_chunk = 0;
+                pf_tile += gridDim.x;
+            }
+        };
+        fetch_next_chunk();
+        uint32_t it = 0, gc = 0;  // stage counter, chunk counter
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            const int tq = tile / p.tiles_d;
-            const int64_t grow = int64_t(tq) * kTileQ + row;
-            const bool row_ok = grow < p.R_q;
-            ProducerLoad cur, nxt;
-            producer_fetch(p, grow, 0, half, row_ok, cur);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                if (kb + 1 < num_kb) producer_fetch(p, grow, kb + 1, half, row_ok, nxt);
+                if ((kb & cs_mask) == 0) {
+                    // chunk turn-over: publish the prefetched registers, start fetching the next chunk
+                    const int buf = gc & 1;
+                    chunk_spill(smem_s + buf * kChunkBytesS, smem_z + buf * kChunkBytesZ, row, half, regs);
+                    fetch_next_chunk();
+                    // every producer must have spilled before anyone reads the new chunk (bounded, like all waits)
+                    mbar_arrive(bar(CHUNK));
+                    if (!(ok = mbar_wait(bar(CHUNK), gc & 1, abort_flag, (3 << 8) | CHUNK))) break;
+                    ++gc;
+                }
+                const int buf = (gc - 1) & 1;
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
-                if (!(ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, (3 << 8) | (EMPTY + s)))) break;
-                producer_store(smem_a + s * kStageBytesA, row, half, cur);
+                if (!(ok = mbar_wait(bar(FULL_C + s), ph, abort_flag, (3 << 8) | (FULL_C + s)))) break;
+                const int j = kb & cs_mask;  // stage inside the chunk
+                const int gi = two_groups ? 4 * j + 2 * half : (p.log2_g == 5 ? 2 * j + half : j);
+                producer_convert(smem_c + s * kStageBytesC, smem_a + s * kStageBytesA, smem_s + buf * kChunkBytesS,
+                                 smem_z + buf * kChunkBytesZ, row, half, gi, two_groups, has_zp);
                 fence_proxy_async();  // make the generic-proxy stores visible to the tensor core
                 mbar_arrive(bar(FULL_A + s));
-                cur = nxt;
             }
         }
     } else {
@@ -471,6 +556,15 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", who, int(cr));
+    // raw codes: [R_q, K] bytes, 64-byte rows in shared memory, no swizzle (read by the producer warps)
+    CUtensorMap cmap;
+    const cuuint64_t cdims[2] = {cuuint64_t(K), cuuint64_t(R_q)};
+    const cuuint64_t cstrides[1] = {cuuint64_t(K)};
+    const cuuint32_t cbox[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileQ)};
+    cr = encode(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(q), cdims, cstrides, cbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled (codes) failed with %d", who, int(cr));
 
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -489,13 +583,16 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     p.R_d = R_d;
     p.K = K;
     p.log2_g = group_size == 16 ? 4 : group_size == 32 ? 5 : 6;
+    p.gpr = K / group_size;
+    p.chunk_vec_ok = p.gpr % 16 == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0 &&
+                     (zp_or_null == nullptr || (reinterpret_cast<uintptr_t>(zp_or_null) & 15) == 0);
     p.transpose_out = quant_is_rhs ? 1 : 0;
     p.tiles_q = int(tiles_q);
     p.tiles_d = int(tiles_d);
     const int64_t num_tiles = tiles_q * tiles_d;
     const int sms = tcb::sm_count();
     const int grid = int(num_tiles < sms ? num_tiles : sms);
-    fused_dequant_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, p);
+    fused_dequant_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
 }
