@@ -58,6 +58,9 @@ constexpr uint32_t kChunkBytesZ = kTileQ * kChunkGroups;                     // 
 constexpr uint32_t kSmemTiles = kStages * (kStageBytesA + kStageBytesB + kStageBytesC) + 2 * (kChunkBytesS + kChunkBytesZ);
 constexpr uint32_t kSmemBytes = kSmemTiles + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr long long kWaitBudgetClocks = 4000000000LL;  // ~2 s at 2 GHz
+constexpr uint32_t kSuspendHintNs = 20000;              // a waiting thread may sleep this long inside one try_wait
+                                                       // (it is woken when the phase completes), so waiters do not
+                                                       // burn issue slots the producer warps need
 
 __device__ int g_status = 0;  // 0 ok; otherwise (role << 8 | barrier id) of the first wait that ran out
 
@@ -78,10 +81,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
