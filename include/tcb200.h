@@ -72,6 +72,32 @@ TCB_API int tcb_decompress_amo(const uint8_t* q, const uint16_t* scales, const u
                        int64_t numel, int group_size, void* stream);
 
 /*
+ * Decode of codes that sit in HOST memory, for callers that must not allocate on
+ * the device.  This entry point has no counterpart in the reference.  It exists
+ * for processes that run under a fixed device-memory plan -- an allocator that
+ * took the whole GPU at start-up, or code that runs while another thread captures
+ * a CUDA graph, when cudaMalloc is off limits -- and therefore cannot provide the
+ * device staging buffers the batch readers ask their caller for.  The staging
+ * lives inside the library instead: a fixed array of about 4.75 MiB in the device
+ * memory of every GPU that loads the library, held until the process exits.
+ *   q_host / scales_host / zp_host   host arrays laid out as for tcb_decompress_amo
+ *                                    (page-locked memory makes the copies asynchronous)
+ *   out_dev                          device output, [numel] bf16 bit patterns
+ * At most TCB_NOALLOC_MAX_VALUES values per call; larger sizes are refused with
+ * TCB_ERR_TOO_LARGE (split the tensor at a multiple of the group size).
+ * The call enqueues three host-to-device copies and the decode kernel on `stream`
+ * and calls no cudaMalloc / cudaFree or any other allocating routine.  The first
+ * call on each device looks up the array's device address (cudaGetSymbolAddress);
+ * make that first call outside any stream capture.  All calls on one device share
+ * the one array, which keeps the previous call's bytes: every byte a call reads
+ * it has overwritten first, so nothing needs clearing, but two calls whose work
+ * overlaps on the GPU (different streams, no ordering between them) race on it.
+ */
+#define TCB_NOALLOC_MAX_VALUES (4 * 1024 * 1024)
+TCB_API int tcb_decompress_amo_host_noalloc(const uint8_t* q_host, const uint16_t* scales_host, const uint8_t* zp_host,
+                                            uint16_t* out_dev, int64_t numel, int group_size, void* stream);
+
+/*
  * AMO-BQ encode, candidate-table presets (fast / balanced / accurate / max or a
  * custom table).  Replaces quantize_int8_amo_bq's search
  * (src/tensorcache/codec.py:774-893; Triton kernel src/tensorcache/fused_ops.py:95-143)

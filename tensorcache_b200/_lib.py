@@ -15,6 +15,7 @@ LIB_PATH = _PKG / "libtcb200.so"
 TCB_OK = 0
 ERR_BAD_ARG, ERR_GROUP_SIZE, ERR_CUDA, ERR_TIMEOUT, ERR_ALIGNMENT, ERR_TOO_LARGE, ERR_IO = 1, 2, 3, 4, 5, 6, 7
 DT_BF16, DT_F16, DT_F32 = 0, 1, 2
+NOALLOC_MAX_VALUES = 4 * 1024 * 1024  # TCB_NOALLOC_MAX_VALUES
 
 _vp, _i64, _i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
 _pp = ctypes.POINTER(ctypes.c_void_p)
@@ -50,6 +51,7 @@ SIGNATURES = {
     "tcb_version": (_i32, []),
     "tcb_last_error": (ctypes.c_char_p, []),
     "tcb_decompress_amo": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
+    "tcb_decompress_amo_host_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_compress_amo": (_i32, [_vp, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tcb_compress_amo_quality": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp]),
     "tcb_fused_dequant_linear": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),

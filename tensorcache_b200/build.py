@@ -30,6 +30,7 @@ SOURCES = [
     ("compress.cu", ["-fmad=false"]),
     ("streamer.cpp", []),
     ("fused_linear.cu", []),
+    ("noalloc.cu", []),
 ]
 
 
