@@ -173,8 +173,14 @@ def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_ran
 
 
 def default_gather_threads() -> int:
+    """Gather workers per reader: the cores this process may use, shared between the ranks of the
+    node when a launcher says how many there are (LOCAL_WORLD_SIZE / WORLD_SIZE), at most 8."""
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    return max(1, min(8, n))
+    try:
+        local_ranks = int(os.environ.get("LOCAL_WORLD_SIZE") or os.environ.get("WORLD_SIZE") or 1)
+    except ValueError:
+        local_ranks = 1
+    return max(1, min(8, n // max(1, local_ranks) - 1))
 
 
 class NativePipeline:

@@ -14,8 +14,11 @@
 //   __fadd_rn / __fsub_rn (never contracted into FMA), rintf() for
 //   round-half-to-even, the first minimum wins (strict <), and the candidate
 //   multipliers are the host's torch.linspace values passed in by value.
-// The kernels are ALU-bound (one IEEE division and ~10 dependent operations per
-// value and candidate); they never synchronise with the host.
+// The kernels are ALU-bound (~12 dependent fp32 operations per value and candidate).
+// The reference's per-value IEEE division x / s is replaced by a multiplication with the
+// candidate's reciprocal plus a guard that falls back to the exact division in the rare
+// case where the two could round to different codes (see quant_index), so the result is
+// still the reference's, bit for bit.  The kernels never synchronise with the host.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -33,6 +36,22 @@ struct CandTable {
 __device__ __forceinline__ bool finite_f32(float v) { return (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u; }
 
 __device__ __forceinline__ float clamp255(float v) { return fminf(fmaxf(v, 0.0f), 255.0f); }
+
+// rint(x / s + zp) with the IEEE quotient, without paying for an IEEE division per value.
+// `r` is the correctly rounded reciprocal of s (one per candidate).  t~ = x * r + zp differs from
+// the reference's t = fl(fl(x / s) + zp) by less than 2^-13 whenever |t~| < 512 (the product is
+// within 2.5 ulp of the quotient, ulp <= 2^-15 there, plus one rounding of the sum on each side),
+// so both round to the same integer unless t~ lies within 2^-12 of a half-integer; only then is the
+// exact division evaluated.  For |t~| >= 512 the two values may differ by more, but both are far
+// outside [0, 255] on the same side and clamp identically whichever path is taken.  NaN (never
+// produced for finite inputs) takes the exact path.
+__device__ __forceinline__ float quant_index(float x, float s, float r, float zp) {
+    const float t = __fadd_rn(__fmul_rn(x, r), zp);
+    float k = rintf(t);
+    const float dist = fabsf(__fsub_rn(t, k));
+    if (!(dist <= 0.5f - 0x1p-12f)) k = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
+    return k;
+}
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
@@ -172,14 +191,19 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
         for (int c = 0; c < tab.n; ++c) {
             const float s = __fmul_rn(s0, tab.m[c]);
             const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
+            const float rcp = __frcp_rn(s);
             float e[VPL];
 #pragma unroll
             for (int k = 0; k < VPL; ++k) {
-                const float t = __fadd_rn(__fdiv_rn(v[k], s), zp);
-                const float qc = clamp255(rintf(t));
+                const float qc = clamp255(quant_index(v[k], s, rcp, zp));
                 const float rec = __fmul_rn(__fsub_rn(qc, zp), s);
-                const float d = ((finmask >> k) & 1u) ? __fsub_rn(v[k], rec) : 0.0f;
+                const float d = __fsub_rn(v[k], rec);
                 e[k] = __fmul_rn(d, d);
+            }
+            if (finmask != (1u << VPL) - 1u) {  // rare: positions that held NaN / Inf do not count
+#pragma unroll
+                for (int k = 0; k < VPL; ++k)
+                    if (!((finmask >> k) & 1u)) e[k] = 0.0f;
             }
             const float err = quad_sum<G>(e, j, lane, qmask);
             if (c == 0 || err < best_err) {
@@ -209,8 +233,8 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
 // ------------------------------------------------------------------ quality mode
 
 // code choice of the reference's _amo_quality_codes for one value
-__device__ __forceinline__ float quality_code(float x, float s, float zp, float& err_out) {
-    const float r = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
+__device__ __forceinline__ float quality_code(float x, float s, float rcp, float zp, float& err_out) {
+    const float r = quant_index(x, s, rcp, zp);
     float qv = clamp255(r);
     float d = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(qv, zp), s)));
     float err = __fmul_rn(d, d);
@@ -275,11 +299,12 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             const int use = bits < hi_bits ? bits : hi_bits;
             const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
             const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
+            const float rcp = __frcp_rn(s);
             float e[VPL];
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
                 float err;
-                (void)quality_code(v[i], s, zp, err);
+                (void)quality_code(v[i], s, rcp, zp, err);
                 e[i] = ((finmask >> i) & 1u) ? err : 0.0f;
             }
             const float tot = quad_sum<G>(e, j, lane, qmask);
@@ -295,7 +320,7 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             float err;
-            const float qf = quality_code(v[i], best_s, best_zp, err);
+            const float qf = quality_code(v[i], best_s, __frcp_rn(best_s), best_zp, err);
             codes[i] = ((finmask >> i) & 1u) ? uint8_t(qf) : zp8;
         }
         store_codes<G>(q, numel, base, j, out_aligned, codes);

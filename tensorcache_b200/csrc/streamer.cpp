@@ -24,6 +24,10 @@
 
 #include "tcb_common.h"
 
+#if defined(__x86_64__)
+#include <immintrin.h>
+#endif
+
 namespace tcb {
 int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,
                       int group_size, cudaStream_t st);
@@ -103,6 +107,48 @@ private:
     bool stop_ = false;
 };
 
+// Row copy into page-locked staging.  The destination is written once and next read by the
+// DMA engine, never by this core, so the stores bypass the cache (non-temporal): no
+// read-for-ownership of the destination lines and no eviction of the source's page-cache
+// lines.  Falls back to memcpy for short or unaligned-tail pieces and on CPUs without AVX2.
+#if defined(__x86_64__)
+__attribute__((target("avx2"))) static void copy_stream_avx2(uint8_t* dst, const uint8_t* src, size_t n) {
+    // head: bring dst to 32-byte alignment
+    size_t head = (32 - (reinterpret_cast<uintptr_t>(dst) & 31)) & 31;
+    if (head > n) head = n;
+    if (head) {
+        std::memcpy(dst, src, head);
+        dst += head; src += head; n -= head;
+    }
+    size_t blocks = n / 128;
+    for (size_t i = 0; i < blocks; ++i) {
+        const __m256i a = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src));
+        const __m256i b = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src + 32));
+        const __m256i c = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src + 64));
+        const __m256i d = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src + 96));
+        _mm256_stream_si256(reinterpret_cast<__m256i*>(dst), a);
+        _mm256_stream_si256(reinterpret_cast<__m256i*>(dst + 32), b);
+        _mm256_stream_si256(reinterpret_cast<__m256i*>(dst + 64), c);
+        _mm256_stream_si256(reinterpret_cast<__m256i*>(dst + 96), d);
+        src += 128; dst += 128;
+    }
+    _mm_sfence();
+    const size_t tail = n - blocks * 128;
+    if (tail) std::memcpy(dst, src, tail);
+}
+#endif
+
+static void copy_row(uint8_t* dst, const uint8_t* src, size_t n) {
+#if defined(__x86_64__)
+    static const bool have_avx2 = __builtin_cpu_supports("avx2");
+    if (have_avx2 && n >= 4096) {
+        copy_stream_avx2(dst, src, n);
+        return;
+    }
+#endif
+    std::memcpy(dst, src, n);
+}
+
 // dst row i <- src_of(i), rows split over the pool.  Rows of a cache are hundreds
 // of KB, so one memcpy per row already streams at full speed.
 template <typename SrcOf>
@@ -112,7 +158,7 @@ void gather_rows(WorkerPool& pool, uint8_t* dst, int64_t row_bytes, int64_t n, c
     if (parts > n) parts = int(n);
     pool.run(parts, [&](int t) {
         const int64_t lo = n * t / parts, hi = n * (t + 1) / parts;
-        for (int64_t i = lo; i < hi; ++i) std::memcpy(dst + i * row_bytes, src_of(i), size_t(row_bytes));
+        for (int64_t i = lo; i < hi; ++i) copy_row(dst + i * row_bytes, src_of(i), size_t(row_bytes));
     });
 }
 

@@ -13,7 +13,9 @@ Differences from the reference, on purpose:
   CPU implementation, which this package does not have); the host-side parts
   (manifest, rank -> shard mapping, ``len``) work without a GPU;
 * ``all_rank_shards=True`` lets a rank read every shard ``i`` with
-  ``i % world_size == rank`` instead of the single shard ``rank % num_shards``.
+  ``i % world_size == rank`` instead of the single shard ``rank % num_shards``;
+* the ring has three slots by default (``ring_slots``; the reference has two), which
+  costs one more batch of staging and output memory and hides the host gather.
 """
 from __future__ import annotations
 
@@ -39,6 +41,7 @@ class ZeroCopyTensorStreamer:
         world_size: Optional[int] = None,
         all_rank_shards: bool = False,
         gather_threads: Optional[int] = None,
+        ring_slots: Optional[int] = None,
     ):
         self.cache_prefix = Path(cache_prefix)
         self.batch_size = int(batch_size)
@@ -63,7 +66,12 @@ class ZeroCopyTensorStreamer:
         self.group_size = lay.group_size
         self.amo_bq = lay.amo_bq
         self.scales_per_sample = lay.groups_per_sample
-        self.n_bufs = 1 if low_vram else 2
+        # ring depth: 1 = serial (low_vram); the default of 3 keeps the gather, the H2D copy and the decode of
+        # three different batches in flight (the reference's ring has 2); a yielded view stays valid until
+        # n_bufs further batches have been requested
+        self.n_bufs = 1 if low_vram else int(ring_slots or 3)
+        if not 1 <= self.n_bufs <= 8:
+            raise ValueError(f"ring_slots {self.n_bufs} outside 1..8")
         self.indices = np.arange(self.num_samples)
         self._gather_threads = gather_threads
         self._pipe: Optional[NativePipeline] = None
@@ -96,7 +104,7 @@ class ZeroCopyTensorStreamer:
             self._pipe = NativePipeline(self._layout, self.batch_size, self.device, self.n_bufs, self._gather_threads)
             self.out_bf16 = self._pipe.dev_out
             self.out_bf16_0 = self.out_bf16[0]
-            self.out_bf16_1 = self.out_bf16[-1]
+            self.out_bf16_1 = self.out_bf16[1] if len(self.out_bf16) > 1 else self.out_bf16[0]
             self.gpu_int8, self.gpu_scales, self.gpu_zp = self._pipe.dev_q, self._pipe.dev_s, self._pipe.dev_zp
             self.pinned_int8, self.pinned_scales, self.pinned_zp = self._pipe.pinned_q, self._pipe.pinned_s, self._pipe.pinned_zp
         return self._pipe

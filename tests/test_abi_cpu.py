@@ -69,6 +69,20 @@ def test_gather_rows(built_lib, nthreads):
     assert built_lib.tcb_gather_rows(None, src.ctypes.data, 1000, None, 0, 5, nthreads) != 0
 
 
+def test_gather_large_rows_take_the_streaming_copy_path(built_lib):
+    """Rows of >= 4 KB are copied with cache-bypassing stores; odd sizes and unaligned
+    destinations exercise its head / tail handling."""
+    rng = np.random.default_rng(1)
+    for row_bytes, off in ((4096, 0), (5003, 0), (342528, 0), (21408, 7), (10704, 1)):
+        src = rng.integers(0, 256, (40, row_bytes), dtype=np.uint8)
+        idx = rng.permutation(40)[:23].astype(np.int64)
+        buf = np.full(23 * row_bytes + 64, 0xAB, np.uint8)
+        dst = buf[off:off + 23 * row_bytes]
+        assert built_lib.tcb_gather_rows(dst.ctypes.data, src.ctypes.data, row_bytes, idx.ctypes.data, 0, 23, 4) == 0
+        assert np.array_equal(dst.reshape(23, row_bytes), src[idx]), (row_bytes, off)
+        assert np.all(buf[:off] == 0xAB) and np.all(buf[off + 23 * row_bytes:] == 0xAB)
+
+
 def test_product_package_does_not_touch_the_oracle():
     """The oracle is test infrastructure; nothing under tensorcache_b200/ may import it."""
     for p in (ROOT / "tensorcache_b200").rglob("*.py"):
