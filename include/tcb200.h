@@ -193,7 +193,19 @@ typedef struct tcb_streamer_desc {
     void* const* dev_s;
     void* const* dev_zp;
     void* const* dev_out;          /* [n_slots] bf16 [batch_size, values_per_sample]         */
+    int direct_dma;                /* != 0: the shard mappings are page-locked (tcb_pin_host_range);
+                                      copies go straight from them, no staging copy of the codes    */
 } tcb_streamer_desc;
+
+/* Page-locks a host range so that the copy engine can read it directly (wraps
+ * cudaHostRegister), and undoes it.  Used for the "resident shard" mode of the
+ * readers: the shard files are mapped privately (copy-on-write) and writable --
+ * the driver refuses read-only and shared file mappings -- and pinned once, which
+ * costs about 0.4 s per GB and as much host memory as the shard; afterwards no
+ * CPU touches the codes again.  The reference always copies rows on the CPU
+ * (src/tensorcache/streamer.py:434-457). */
+TCB_API int tcb_pin_host_range(void* p, int64_t bytes);
+TCB_API int tcb_unpin_host_range(void* p);
 
 /* Creates the pipeline on the current device.  The tables of the descriptor are
  * copied; the buffers and mappings they name must stay valid until destroy. */

@@ -43,6 +43,7 @@ class StreamerDesc(ctypes.Structure):
         ("dev_s", _pp),
         ("dev_zp", _pp),
         ("dev_out", _pp),
+        ("direct_dma", _i32),
     ]
 
 
@@ -57,6 +58,8 @@ SIGNATURES = {
     "tcb_fused_dequant_linear": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tcb_fused_dequant_linear_check": (_i32, [_vp]),
     "tcb_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i32]),
+    "tcb_pin_host_range": (_i32, [_vp, _i64]),
+    "tcb_unpin_host_range": (_i32, [_vp]),
     "tcb_streamer_create": (_i32, [ctypes.POINTER(StreamerDesc), ctypes.POINTER(_vp)]),
     "tcb_streamer_num_samples": (_i32, [_vp, ctypes.POINTER(_i64)]),
     "tcb_streamer_begin": (_i32, [_vp, _vp, _i64]),

@@ -37,6 +37,7 @@ class CacheLayout:
     shards: List[ShardFiles] = field(default_factory=list)
     total_shards_on_disk: int = 1
     selected: Optional[List[int]] = None   # shard numbers opened, None = unsharded cache
+    private: bool = False                   # mapped copy-on-write so that the mappings can be page-locked
 
     @property
     def groups_per_sample(self) -> int:
@@ -81,7 +82,7 @@ class CacheLayout:
                 setattr(sh, name, None)
 
 
-def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq: bool) -> ShardFiles:
+def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq: bool, private: bool = False) -> ShardFiles:
     if not amo_bq:
         raise NotImplementedError("this cache was written with the symmetric INT8 codec; only AMO-BQ caches "
                                   "(amo_bq=True) are readable on the B200 path")
@@ -95,9 +96,12 @@ def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq
             have = os.path.getsize(path)
             if have < nbytes:
                 raise ValueError(f"cache file {path!r} is truncated: {have} bytes, {nbytes} needed for {n} samples")
-        sh.q = np.memmap(prefix + "_int8.bin", dtype=np.uint8, mode="r", shape=(n, seq_len, dim))
-        sh.s = np.memmap(prefix + "_scales.bin", dtype=np.uint16, mode="r", shape=(n, groups))
-        sh.zp = np.memmap(prefix + "_zp.bin", dtype=np.uint8, mode="r", shape=(n, groups))
+        # "c" = private copy-on-write mapping: never written here, but the only kind of file mapping
+        # the CUDA driver agrees to page-lock (resident-shard mode of the readers)
+        mode = "c" if private else "r"
+        sh.q = np.memmap(prefix + "_int8.bin", dtype=np.uint8, mode=mode, shape=(n, seq_len, dim))
+        sh.s = np.memmap(prefix + "_scales.bin", dtype=np.uint16, mode=mode, shape=(n, groups))
+        sh.zp = np.memmap(prefix + "_zp.bin", dtype=np.uint8, mode=mode, shape=(n, groups))
     return sh
 
 
@@ -126,7 +130,7 @@ def resolve_shards(num_shards: int, shard_idx: Optional[int], rank: Optional[int
     return None
 
 
-def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_rank_shards=False) -> CacheLayout:
+def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_rank_shards=False, private=False) -> CacheLayout:
     """Parses ``<prefix>_shards.json`` or ``<prefix>_meta.json`` and maps the files."""
     prefix = str(cache_prefix)
     manifest_path = prefix + "_shards.json"
@@ -144,7 +148,8 @@ def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_ran
         amo = man.get("amo_bq", False)
         groups = (seq_len * dim + G - 1) // G
         sizes = list(man.get("shard_sizes") or [])
-        lay = CacheLayout(man, seq_len, dim, G, amo, [], n_shards, selected if selected is not None else list(range(n_shards)))
+        lay = CacheLayout(man, seq_len, dim, G, amo, [], n_shards, selected if selected is not None else list(range(n_shards)),
+                          private)
         for i in lay.selected:
             n = None
             mp = prefixes[i] + "_meta.json"
@@ -156,7 +161,7 @@ def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_ran
                     lay.meta = sm
             if n is None:
                 n = sizes[i] if sizes else man["num_samples"] // n_shards
-            lay.shards.append(_open_shard(prefixes[i], n, seq_len, dim, groups, amo))
+            lay.shards.append(_open_shard(prefixes[i], n, seq_len, dim, groups, amo, private))
         return lay
     # rank / world_size on an unsharded cache are ignored, as the reference's streamer does
     if shard_idx not in (None, 0):
@@ -167,8 +172,8 @@ def open_cache(cache_prefix, shard_idx=None, rank=None, world_size=None, all_ran
     seq_len, dim, G = meta["seq_len"], meta["dim"], meta["group_size"]
     amo = meta.get("amo_bq", False)
     groups = (seq_len * dim + G - 1) // G
-    lay = CacheLayout(meta, seq_len, dim, G, amo, [], 1, None)
-    lay.shards.append(_open_shard(prefix, meta["num_samples"], seq_len, dim, groups, amo))
+    lay = CacheLayout(meta, seq_len, dim, G, amo, [], 1, None, private)
+    lay.shards.append(_open_shard(prefix, meta["num_samples"], seq_len, dim, groups, amo, private))
     return lay
 
 
@@ -187,7 +192,7 @@ class NativePipeline:
     """Owns the ring buffers (torch tensors) and the native streamer handle."""
 
     def __init__(self, layout: CacheLayout, batch_size: int, device: torch.device, n_slots: int,
-                 n_threads: Optional[int] = None):
+                 n_threads: Optional[int] = None, pin_shards: bool = False):
         if device.type != "cuda":
             raise RuntimeError("the batch readers decode on a CUDA device only (no CPU decode path)")
         if not torch.cuda.is_available():
@@ -199,7 +204,26 @@ class NativePipeline:
         vps = layout.seq_len * layout.dim
         gps = layout.groups_per_sample
         B = self.batch_size
-        self.pinned_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
+        self.pin_shards = bool(pin_shards)
+        self._pinned_ranges = []
+        if self.pin_shards:
+            if not layout.private:
+                raise ValueError("pin_shards needs a cache opened with private=True (copy-on-write mappings)")
+            with torch.cuda.device(device):
+                try:
+                    for sh in layout.shards:
+                        if sh.num_samples == 0:
+                            continue
+                        for arr in (sh.q, sh.s, sh.zp):
+                            nbytes = (arr.nbytes + 4095) // 4096 * 4096   # the mapping covers whole pages
+                            _lib.check(_lib.lib().tcb_pin_host_range(ctypes.c_void_p(arr.ctypes.data), nbytes))
+                            self._pinned_ranges.append(arr.ctypes.data)
+                except Exception:
+                    self._unpin()
+                    raise
+        # the staging copy of the codes is not needed when the copy engine reads the shard itself
+        self.pinned_q = [] if self.pin_shards else [
+            torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
         self.pinned_s = [torch.empty((B, gps), dtype=torch.bfloat16, pin_memory=True) for _ in range(n_slots)]
         self.pinned_zp = [torch.empty((B, gps), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
         self.dev_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, device=device) for _ in range(n_slots)]
@@ -208,6 +232,8 @@ class NativePipeline:
         self.dev_out = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
 
         def table(tensors):
+            if not tensors:
+                return (ctypes.c_void_p * n_slots)(*([None] * n_slots))
             return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
         def base_table(name):
@@ -227,6 +253,7 @@ class NativePipeline:
         d.batch_size = B
         d.n_slots = n_slots
         d.n_threads = n_threads or default_gather_threads()
+        d.direct_dma = 1 if self.pin_shards else 0
         (d.pinned_q, d.pinned_s, d.pinned_zp, d.dev_q, d.dev_s, d.dev_zp, d.dev_out) = self._tables
         self._handle = ctypes.c_void_p()
         with torch.cuda.device(device):
@@ -259,10 +286,18 @@ class NativePipeline:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().tcb_streamer_release(self._handle, self._stream()))
 
+    def _unpin(self):
+        for addr in self._pinned_ranges:
+            _lib.lib().tcb_unpin_host_range(ctypes.c_void_p(addr))
+        self._pinned_ranges = []
+
     def close(self):
         if getattr(self, "_handle", None) is not None and self._handle.value:
             _lib.lib().tcb_streamer_destroy(self._handle)
             self._handle = ctypes.c_void_p()
+        if getattr(self, "_pinned_ranges", None):
+            with torch.cuda.device(self.device):
+                self._unpin()
         for name in ("pinned_q", "pinned_s", "pinned_zp", "dev_q", "dev_s", "dev_zp", "dev_out"):
             setattr(self, name, None)
 

@@ -286,17 +286,63 @@ void producer_main(tcb_streamer* s) {
                     return bases[sh] + local * row_bytes;
                 };
             };
-            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_q[slot]), qrow, rows, src(s->q_bases, qrow));
-            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
-            gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+            if (!s->d.direct_dma) {
+                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_q[slot]), qrow, rows, src(s->q_bases, qrow));
+                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
+                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+            }
             // the consumer's last read of this device slot (this pass or the one before)
             e = cudaStreamWaitEvent(s->copy_stream, s->released[slot], 0);
             if (e != cudaSuccess) { producer_fail(s, e, "cudaStreamWaitEvent(released)"); break; }
-            e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
-            if (e == cudaSuccess)
-                e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
-            if (e == cudaSuccess)
-                e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+            if (!s->d.direct_dma) {
+                e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+            } else {
+                // The mapped shards are page-locked: the copy engine reads them directly.  Runs of
+                // consecutive rows of one shard become one copy.  Codes always go straight from the
+                // mapping (rows are hundreds of KB); when the order is scattered the small side
+                // arrays are gathered by the CPU first so that they cost one copy each, not one per row.
+                std::vector<int64_t> run_first, run_len;   // in units of batch rows
+                std::vector<int> run_shard;
+                std::vector<int64_t> run_local;
+                for (int64_t i = 0; i < rows; ++i) {
+                    int sh;
+                    int64_t local;
+                    locate(s, idx ? idx[i] : first + i, sh, local);
+                    if (!run_first.empty() && run_shard.back() == sh && run_local.back() + run_len.back() == local) {
+                        ++run_len.back();
+                    } else {
+                        run_first.push_back(i);
+                        run_len.push_back(1);
+                        run_shard.push_back(sh);
+                        run_local.push_back(local);
+                    }
+                }
+                const bool scattered = run_first.size() > 8;
+                if (scattered) {
+                    gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
+                    gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+                }
+                for (size_t r = 0; e == cudaSuccess && r < run_first.size(); ++r) {
+                    const int sh = run_shard[r];
+                    const int64_t at = run_first[r], n = run_len[r], loc = run_local[r];
+                    e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_q[slot]) + at * qrow, s->q_bases[sh] + loc * qrow, size_t(n * qrow),
+                                        cudaMemcpyHostToDevice, s->copy_stream);
+                    if (!scattered && e == cudaSuccess)
+                        e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_s[slot]) + at * srow, s->s_bases[sh] + loc * srow, size_t(n * srow),
+                                            cudaMemcpyHostToDevice, s->copy_stream);
+                    if (!scattered && e == cudaSuccess)
+                        e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_zp[slot]) + at * zrow, s->zp_bases[sh] + loc * zrow, size_t(n * zrow),
+                                            cudaMemcpyHostToDevice, s->copy_stream);
+                }
+                if (scattered && e == cudaSuccess)
+                    e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
+                if (scattered && e == cudaSuccess)
+                    e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+            }
             if (e == cudaSuccess) e = cudaEventRecord(s->h2d_done[slot], s->copy_stream);
             if (e != cudaSuccess) { producer_fail(s, e, "H2D enqueue"); break; }
             {
@@ -329,6 +375,27 @@ int quiesce(tcb_streamer* s) {
 
 }  // namespace
 
+extern "C" int tcb_pin_host_range(void* p, int64_t bytes) {
+    if (!p || bytes <= 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_pin_host_range: null pointer or empty range");
+    cudaError_t e = cudaHostRegister(p, size_t(bytes), cudaHostRegisterPortable);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tcb::fail(TCB_ERR_CUDA, "tcb_pin_host_range: cudaHostRegister(%lld bytes): %s (read-only and shared file mappings "
+                         "cannot be page-locked; map the file privately and writable)", (long long)bytes, cudaGetErrorString(e));
+    }
+    return TCB_OK;
+}
+
+extern "C" int tcb_unpin_host_range(void* p) {
+    if (!p) return TCB_OK;
+    cudaError_t e = cudaHostUnregister(p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tcb::cuda_fail(e, "tcb_unpin_host_range: cudaHostUnregister");
+    }
+    return TCB_OK;
+}
+
 extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer** out) {
     if (!desc || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null argument");
     *out = nullptr;
@@ -353,7 +420,7 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
     if (!desc->pinned_q || !desc->pinned_s || !desc->pinned_zp || !desc->dev_q || !desc->dev_s || !desc->dev_zp || !desc->dev_out)
         return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer table");
     for (int i = 0; i < desc->n_slots; ++i)
-        if (!desc->pinned_q[i] || !desc->pinned_s[i] || !desc->pinned_zp[i] || !desc->dev_q[i] || !desc->dev_s[i] ||
+        if ((!desc->pinned_q[i] && !desc->direct_dma) || !desc->pinned_s[i] || !desc->pinned_zp[i] || !desc->dev_q[i] || !desc->dev_s[i] ||
             !desc->dev_zp[i] || !desc->dev_out[i])
             return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer in slot %d", i);
 

@@ -14,6 +14,11 @@ Differences from the reference, on purpose:
   (manifest, rank -> shard mapping, ``len``) work without a GPU;
 * ``all_rank_shards=True`` lets a rank read every shard ``i`` with
   ``i % world_size == rank`` instead of the single shard ``rank % num_shards``;
+* ``pin_shard=True`` keeps the opened shard(s) resident and page-locked in host memory
+  (a private mapping of the files, pinned once at about 0.4 s per GB, costing as much RAM
+  as the shard) so that the copy engine reads the rows itself and no CPU copy remains;
+  the default ``False`` keeps the reference's small-footprint behaviour (rows are copied
+  into page-locked staging by worker threads);
 * the ring has three slots by default (``ring_slots``; the reference has two), which
   costs one more batch of staging and output memory and hides the host gather.
 """
@@ -42,6 +47,7 @@ class ZeroCopyTensorStreamer:
         all_rank_shards: bool = False,
         gather_threads: Optional[int] = None,
         ring_slots: Optional[int] = None,
+        pin_shard: bool = False,
     ):
         self.cache_prefix = Path(cache_prefix)
         self.batch_size = int(batch_size)
@@ -50,7 +56,8 @@ class ZeroCopyTensorStreamer:
         self.low_vram = low_vram
         self.rank = rank
         self.world_size = world_size
-        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards)
+        self.pin_shard = bool(pin_shard)
+        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards, private=self.pin_shard)
         lay = self._layout
         self.meta = lay.meta
         self.is_sharded = lay.selected is not None and len(lay.shards) > 1
@@ -101,7 +108,8 @@ class ZeroCopyTensorStreamer:
         if self._closed:
             raise RuntimeError("streamer is closed")
         if self._pipe is None:
-            self._pipe = NativePipeline(self._layout, self.batch_size, self.device, self.n_bufs, self._gather_threads)
+            self._pipe = NativePipeline(self._layout, self.batch_size, self.device, self.n_bufs, self._gather_threads,
+                                        pin_shards=self.pin_shard)
             self.out_bf16 = self._pipe.dev_out
             self.out_bf16_0 = self.out_bf16[0]
             self.out_bf16_1 = self.out_bf16[1] if len(self.out_bf16) > 1 else self.out_bf16[0]

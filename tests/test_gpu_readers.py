@@ -132,3 +132,28 @@ def test_larger_cache_round_trip_and_early_exit(tmp_path):
     with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False, shard_idx=1) as st:
         got = bits(torch.cat([b.clone() for b in st])).reshape(160, -1)
         assert np.array_equal(got, want[160:])
+
+
+def test_resident_shard_mode_reads_the_same_batches(tmp_path, golden_rows):
+    """pin_shard=True: the shard mappings are page-locked and the copy engine reads rows directly.
+    Same bits as the staging path, contiguous (few long runs) and shuffled (one copy per row)."""
+    want7 = np.concatenate([golden_rows[f"cache_sharded/{i}/rec"] for i in range(7)])
+    with tc.ZeroCopyTensorStreamer(GOLDEN / "cache_sharded" / "feat", batch_size=3, device=DEV, shuffle=False, pin_shard=True) as st:
+        for _ in range(2):
+            assert np.array_equal(bits(torch.cat([b.clone() for b in st])), want7)
+    x = synth.config0_style(41, (300, 32, 256))
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 300, 32, 256, group_size=32, amo_bq=True, amo_mode="fast", num_shards=3)
+    w.append(x.to(DEV)); w.close()
+    q, s, zp, _ = tc.compress(x.to(DEV), "fast", 32)
+    want = bits(tc.decompress(q, s, (300, 32, 256), zp, 32)).reshape(300, -1)
+    with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False, pin_shard=True) as st:
+        assert st.pin_shard and len(st) == 5
+        assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(300, -1), want)
+        st.shuffle = True
+        np.random.seed(5)
+        got = bits(torch.cat([b.clone() for b in st])).reshape(300, -1)
+        assert np.array_equal(got, want[st.indices])
+    with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=50, device=DEV, shuffle=True, pin_shard=True, rank=2, world_size=3) as st:
+        np.random.seed(6)
+        got = bits(torch.cat([b.clone() for b in st])).reshape(100, -1)
+        assert np.array_equal(got, want[200:][st.indices])
