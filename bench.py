@@ -353,6 +353,7 @@ def main():
     ap.add_argument("--impl", default="tcb200", choices=["tcb200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=0, help="batches timed through the streamer (default: min(steps, 200))")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed decodes one by one instead of replaying CUDA graphs")
     ap.add_argument("--decode-only", action="store_true", help="skip the streamer / e2e leg (for profiler captures)")
     ap.add_argument("--workload", default="decode", choices=["decode", "fused_linear", "compress"],
                     help="decode (default) is the headline metric; the other two time the remaining kernels of the path")
@@ -402,15 +403,39 @@ def main():
         sets.append((q, s, zp, torch.empty(SHAPE, dtype=torch.bfloat16, device=device)))
     stream = torch.cuda.current_stream(device)
 
-    def step(i):
-        q, s, zp, out = sets[i % n_sets]
-        rc = L.tcb_decompress_amo(q.data_ptr(), s.data_ptr(), zp.data_ptr(), out.data_ptr(), numel, G, stream.cuda_stream)
+    # plain integers once, so that a launch costs one ctypes call and nothing else on the host
+    ptrs = [(q.data_ptr(), s.data_ptr(), zp.data_ptr(), out.data_ptr()) for q, s, zp, out in sets]
+
+    def step(i, stream_handle):
+        qp, sp, zpp, op = ptrs[i % n_sets]
+        rc = L.tcb_decompress_amo(qp, sp, zpp, op, numel, G, stream_handle)
         if rc != 0:
             _lib.check(rc)
 
     for i in range(args.warmup):
-        step(i)
+        step(i, stream.cuda_stream)
     torch.cuda.synchronize(device)
+
+    # The K timed launches are replayed from CUDA graphs of up to GRAPH_LAUNCHES launches each (plus a
+    # remainder graph), so that the host's launch rate cannot become the limit when many ranks share few cores.
+    GRAPH_LAUNCHES = n_sets * 25
+    graphs = {}
+    if not args.no_graph:
+        side = torch.cuda.Stream(device)
+        for n in {min(GRAPH_LAUNCHES, args.steps), args.steps % GRAPH_LAUNCHES}:
+            if n <= 0:
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                h = torch.cuda.current_stream(device).cuda_stream
+                for i in range(n):
+                    step(i, h)
+            graphs[n] = g
+        torch.cuda.synchronize(device)
+        for g in graphs.values():   # one untimed replay each
+            g.replay()
+        torch.cuda.synchronize(device)
+
     sampler = ClockSampler(physical_gpu_index(local))
     if rank == 0:
         sampler.start()
@@ -418,8 +443,15 @@ def main():
     torch.cuda.synchronize(device)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
-    for i in range(args.steps):
-        step(i)
+    if graphs:
+        full, rest = divmod(args.steps, GRAPH_LAUNCHES)
+        for _ in range(full):
+            graphs[GRAPH_LAUNCHES].replay()
+        if rest:
+            graphs[rest].replay()
+    else:
+        for i in range(args.steps):
+            step(i, stream.cuda_stream)
     ev1.record(stream)
     torch.cuda.synchronize(device)
     barrier()
@@ -469,6 +501,7 @@ def main():
             "dtype": "u8->bf16 (fp32 arithmetic)", "data": "synthetic",
             "config": {"workload": "AMO-BQ G32 decode of [128,446,768] bf16 codes into a preallocated buffer",
                        "group_size": G, "values_per_step_per_gpu": numel, "algorithmic_bytes_per_step": bytes_per_step,
+                       "launch": "eager" if args.no_graph else f"CUDA graphs of {GRAPH_LAUNCHES} launches",
                        "l2_policy": f"{n_sets} rotating input/output sets ({n_sets * bytes_per_step / 1e6:.0f} MB) > 126 MB L2",
                        "parallelism": f"{world} independent replicas, one per GPU, no collective"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,

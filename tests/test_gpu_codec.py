@@ -300,3 +300,22 @@ def test_encoder_is_cuda_graph_capturable(dev):
         torch.cuda.synchronize(dev)
         q2, s2, zp2, _ = tc.compress(y, mode, G)
         assert torch.equal(q, q2) and torch.equal(s.view(torch.int16), s2.view(torch.int16)) and torch.equal(zp, zp2)
+
+
+def test_decoder_is_cuda_graph_capturable(dev):
+    """The decode launch carries a programmatic-dependent-launch attribute; it must still capture and replay."""
+    import tensorcache_b200 as tc
+
+    x = synth.config0_style(33, (8, 64, 128)).to(dev)
+    q, s, zp, shape = tc.compress(x, "balanced", 32)
+    want = tc.decompress(q, s, shape, zp, 32)
+    out = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(3):
+            tc.dequantize_int8_amo_bq(q, s, zp, shape, 32, out_buffer=out)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
