@@ -194,6 +194,32 @@ extern "C" int tcb_gather_rows(void* dst, const void* src_base, int64_t row_byte
 
 // ------------------------------------------------------------------ streamer
 
+// Resident-shard mode, scattered order: one kernel pulls the batch's rows straight out of the
+// page-locked host mapping over PCIe (the SMs issue the reads; a handful of blocks keeps enough
+// 16-byte loads in flight to fill the link) and writes them, packed, into device staging.
+// `rows` is a table of host pointers that itself lives in mapped page-locked memory.
+__global__ void __launch_bounds__(256)
+gather_host_rows_kernel(uint4* __restrict__ dst, const uint4* const* __restrict__ rows, int64_t units_per_row, int64_t n_rows) {
+    const int64_t total = units_per_row * n_rows;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t u0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u0 < total; u0 += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t u = u0 + k * stride;
+            if (u < total) {
+                const int64_t r = u / units_per_row;
+                v[k] = rows[r][u - r * units_per_row];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t u = u0 + k * stride;
+            if (u < total) dst[u] = v[k];
+        }
+    }
+}
+
 struct tcb_streamer {
     tcb_streamer_desc d{};
     std::vector<const uint8_t*> q_bases, s_bases, zp_bases;
@@ -203,6 +229,11 @@ struct tcb_streamer {
     cudaStream_t copy_stream = nullptr;
     std::vector<cudaEvent_t> h2d_done, released;
     WorkerPool* pool = nullptr;
+    // resident mode: per slot three tables of row pointers (codes, scales, zero points) in mapped pinned memory
+    const uint4** row_tables = nullptr;       // host view
+    const uint4** row_tables_dev = nullptr;   // the same memory as the device addresses it
+    std::vector<const uint8_t*> q_dev, s_dev, zp_dev;  // device views of the page-locked mappings
+    bool rows_vectorisable = false;
 
     std::thread producer;
     std::mutex mu;
@@ -322,26 +353,47 @@ void producer_main(tcb_streamer* s) {
                     }
                 }
                 const bool scattered = run_first.size() > 8;
-                if (scattered) {
-                    gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
-                    gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
-                }
-                for (size_t r = 0; e == cudaSuccess && r < run_first.size(); ++r) {
-                    const int sh = run_shard[r];
-                    const int64_t at = run_first[r], n = run_len[r], loc = run_local[r];
-                    e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_q[slot]) + at * qrow, s->q_bases[sh] + loc * qrow, size_t(n * qrow),
-                                        cudaMemcpyHostToDevice, s->copy_stream);
-                    if (!scattered && e == cudaSuccess)
-                        e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_s[slot]) + at * srow, s->s_bases[sh] + loc * srow, size_t(n * srow),
+                if (scattered && s->rows_vectorisable) {
+                    const int64_t B = s->d.batch_size;
+                    const int64_t o = int64_t(slot) * 3 * B;
+                    const uint4** tq = s->row_tables + o;
+                    const uint4** ts = tq + B;
+                    const uint4** tz = ts + B;
+                    for (int64_t i = 0; i < rows; ++i) {
+                        int sh;
+                        int64_t local;
+                        locate(s, idx ? idx[i] : first + i, sh, local);
+                        tq[i] = reinterpret_cast<const uint4*>(s->q_dev[sh] + local * qrow);
+                        ts[i] = reinterpret_cast<const uint4*>(s->s_dev[sh] + local * srow);
+                        tz[i] = reinterpret_cast<const uint4*>(s->zp_dev[sh] + local * zrow);
+                    }
+                    const uint4** dq = s->row_tables_dev + o;
+                    gather_host_rows_kernel<<<48, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_q[slot]), dq, qrow / 16, rows);
+                    gather_host_rows_kernel<<<8, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_s[slot]), dq + B, srow / 16, rows);
+                    gather_host_rows_kernel<<<8, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_zp[slot]), dq + 2 * B, zrow / 16, rows);
+                    e = cudaGetLastError();
+                } else {
+                    if (scattered) {
+                        gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
+                        gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+                    }
+                    for (size_t r = 0; e == cudaSuccess && r < run_first.size(); ++r) {
+                        const int sh = run_shard[r];
+                        const int64_t at = run_first[r], n = run_len[r], loc = run_local[r];
+                        e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_q[slot]) + at * qrow, s->q_bases[sh] + loc * qrow, size_t(n * qrow),
                                             cudaMemcpyHostToDevice, s->copy_stream);
-                    if (!scattered && e == cudaSuccess)
-                        e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_zp[slot]) + at * zrow, s->zp_bases[sh] + loc * zrow, size_t(n * zrow),
-                                            cudaMemcpyHostToDevice, s->copy_stream);
+                        if (!scattered && e == cudaSuccess)
+                            e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_s[slot]) + at * srow, s->s_bases[sh] + loc * srow, size_t(n * srow),
+                                                cudaMemcpyHostToDevice, s->copy_stream);
+                        if (!scattered && e == cudaSuccess)
+                            e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_zp[slot]) + at * zrow, s->zp_bases[sh] + loc * zrow, size_t(n * zrow),
+                                                cudaMemcpyHostToDevice, s->copy_stream);
+                    }
+                    if (scattered && e == cudaSuccess)
+                        e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
+                    if (scattered && e == cudaSuccess)
+                        e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
                 }
-                if (scattered && e == cudaSuccess)
-                    e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
-                if (scattered && e == cudaSuccess)
-                    e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
             }
             if (e == cudaSuccess) e = cudaEventRecord(s->h2d_done[slot], s->copy_stream);
             if (e != cudaSuccess) { producer_fail(s, e, "H2D enqueue"); break; }
@@ -377,7 +429,7 @@ int quiesce(tcb_streamer* s) {
 
 extern "C" int tcb_pin_host_range(void* p, int64_t bytes) {
     if (!p || bytes <= 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_pin_host_range: null pointer or empty range");
-    cudaError_t e = cudaHostRegister(p, size_t(bytes), cudaHostRegisterPortable);
+    cudaError_t e = cudaHostRegister(p, size_t(bytes), cudaHostRegisterPortable | cudaHostRegisterMapped);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return tcb::fail(TCB_ERR_CUDA, "tcb_pin_host_range: cudaHostRegister(%lld bytes): %s (read-only and shared file mappings "
@@ -464,6 +516,43 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
         if (s->copy_stream) cudaStreamDestroy(s->copy_stream);
         delete s;
         return rc;
+    }
+    if (desc->direct_dma) {
+        // the gather kernel moves 16-byte units: rows and mapping bases must be multiples of 16 bytes
+        bool ok16 = desc->values_per_sample % 16 == 0 && (desc->groups_per_sample * 2) % 16 == 0 && desc->groups_per_sample % 16 == 0;
+        for (int i = 0; i < desc->n_shards; ++i)
+            ok16 = ok16 && ((reinterpret_cast<uintptr_t>(s->q_bases[i]) | reinterpret_cast<uintptr_t>(s->s_bases[i]) |
+                             reinterpret_cast<uintptr_t>(s->zp_bases[i])) & 15) == 0;
+        for (int i = 0; i < desc->n_slots; ++i)
+            ok16 = ok16 && ((reinterpret_cast<uintptr_t>(s->dev_q[i]) | reinterpret_cast<uintptr_t>(s->dev_s[i]) |
+                             reinterpret_cast<uintptr_t>(s->dev_zp[i])) & 15) == 0;
+        // device-side addresses of the mappings (they were registered as mapped memory)
+        for (int i = 0; ok16 && i < desc->n_shards; ++i) {
+            void *dq = nullptr, *ds = nullptr, *dz = nullptr;
+            if (desc->shard_sizes[i] > 0 &&
+                (cudaHostGetDevicePointer(&dq, const_cast<uint8_t*>(s->q_bases[i]), 0) != cudaSuccess ||
+                 cudaHostGetDevicePointer(&ds, const_cast<uint8_t*>(s->s_bases[i]), 0) != cudaSuccess ||
+                 cudaHostGetDevicePointer(&dz, const_cast<uint8_t*>(s->zp_bases[i]), 0) != cudaSuccess)) {
+                cudaGetLastError();
+                ok16 = false;
+            }
+            s->q_dev.push_back(static_cast<const uint8_t*>(dq));
+            s->s_dev.push_back(static_cast<const uint8_t*>(ds));
+            s->zp_dev.push_back(static_cast<const uint8_t*>(dz));
+        }
+        if (ok16) {
+            void *t = nullptr, *td = nullptr;
+            const size_t bytes = size_t(desc->n_slots) * 3 * size_t(desc->batch_size) * sizeof(void*);
+            if (cudaHostAlloc(&t, bytes, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess &&
+                cudaHostGetDevicePointer(&td, t, 0) == cudaSuccess) {
+                s->row_tables = static_cast<const uint4**>(t);
+                s->row_tables_dev = static_cast<const uint4**>(td);
+                s->rows_vectorisable = true;
+            } else {
+                cudaGetLastError();  // fall back to one copy per row
+                if (t) cudaFreeHost(t);
+            }
+        }
     }
     int nt = desc->n_threads < 1 ? 1 : desc->n_threads > 64 ? 64 : desc->n_threads;
     s->pool = new WorkerPool(nt - 1);
@@ -575,6 +664,7 @@ extern "C" int tcb_streamer_destroy(tcb_streamer* s) {
     for (auto ev : s->h2d_done) cudaEventDestroy(ev);
     for (auto ev : s->released) cudaEventDestroy(ev);
     cudaStreamDestroy(s->copy_stream);
+    if (s->row_tables) cudaFreeHost(const_cast<uint4**>(s->row_tables));
     delete s->pool;
     delete s;
     return TCB_OK;
