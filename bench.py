@@ -384,12 +384,33 @@ def main():
         if world > 1:
             dist.barrier()
 
-    def max_over_ranks(x: float) -> float:
+    def reduce_over_ranks(x: float, op) -> float:
         if world == 1:
             return x
         t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=op)
         return float(t.item())
+
+    def max_over_ranks(x: float) -> float:
+        return reduce_over_ranks(x, dist.ReduceOp.MAX)
+
+    def pinned_h2d_rate():
+        """Plain pinned-memory H2D copy rate of this rank while every other rank does the same:
+        the ceiling of the reader path on this box at this number of GPUs."""
+        nbytes = 256 << 20
+        h = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        d = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        d.copy_(h, non_blocking=True)
+        torch.cuda.synchronize(device)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(8):
+            d.copy_(h, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize(device)
+        barrier()
+        return 8 * nbytes / (e0.elapsed_time(e1) / 1e3) / 1e9
 
     import tensorcache_b200 as tc
     from tensorcache_b200 import _lib
@@ -483,6 +504,14 @@ def main():
     e2e_value = None if args.decode_only else bytes_per_step * e2e_steps * world / r_contig / 1e9
 
     clocks = sampler.stop() if rank == 0 else None   # sampled over the decode loop and the streamer passes
+    pcie = None
+    if not args.decode_only:
+        mine = pinned_h2d_rate()
+        pcie = {"pinned_h2d_gbs_per_gpu_min": reduce_over_ranks(mine, dist.ReduceOp.MIN),
+                "pinned_h2d_gbs_sum": reduce_over_ranks(mine, dist.ReduceOp.SUM),
+                "note": "plain 256 MB pinned-memory copies issued by all ranks at once; the reader path moves "
+                        "374,640 compressed bytes per sample over this link"}
+        pcie["ceiling_samples_per_s"] = pcie["pinned_h2d_gbs_sum"] * 1e9 / 374640.0
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
@@ -520,6 +549,7 @@ def main():
                 "resident_contiguous_samples_per_s": SHAPE[0] * e2e_steps * world / r_contig,
                 "resident_random_samples_per_s": SHAPE[0] * e2e_steps * world / r_random,
                 "shard_samples_per_rank": 8 * SHAPE[0], "batch_size": SHAPE[0]},
+            "pcie": pcie,
             "cpu_baseline": cpu,
             "gpu_launches": args.steps,
             "clocks": clocks,

@@ -147,6 +147,14 @@ TCB_API int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q, co
  * bounded wait runs out.  Synchronises `stream`.  Returns TCB_OK or TCB_ERR_TIMEOUT. */
 TCB_API int tcb_fused_dequant_linear_check(void* stream);
 
+/* Launches a tiny kernel whose only work is a bounded wait on a barrier that nothing
+ * ever signals, with a budget of `budget_ms` milliseconds (1..1000).  The kernel
+ * gives up when the budget is spent, releases its second waiter through the abort
+ * flag and returns; tcb_fused_dequant_linear_check() then reports TCB_ERR_TIMEOUT.
+ * Exercises the time-out path every wait of the fused GEMM uses, without hanging or
+ * faulting the device.  (No counterpart in the reference, which has no device waits.) */
+TCB_API int tcb_selftest_bounded_wait(int budget_ms, void* stream);
+
 /*
  * Host-side row gather used by the batch readers: copies n rows of row_bytes
  * bytes, dst[i] = src_base[idx[i]] (idx == NULL: rows first_row .. first_row+n-1,

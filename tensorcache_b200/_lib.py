@@ -57,6 +57,7 @@ SIGNATURES = {
     "tcb_compress_amo_quality": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp]),
     "tcb_fused_dequant_linear": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tcb_fused_dequant_linear_check": (_i32, [_vp]),
+    "tcb_selftest_bounded_wait": (_i32, [_i32, _vp]),
     "tcb_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i32]),
     "tcb_pin_host_range": (_i32, [_vp, _i64]),
     "tcb_unpin_host_range": (_i32, [_vp]),

@@ -90,7 +90,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false if the CTA is aborting (or this wait ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who,
+                                          long long budget = kWaitBudgetClocks) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -98,7 +99,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudgetClocks) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1;
             atomicCAS(&g_status, 0, who);
             return false;
@@ -510,6 +511,30 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
     }
 }
 
+// Self-test of the bounded wait: warp 0 waits on a barrier nobody ever arrives on, with a short
+// clock budget; warp 1 waits on a second such barrier with the full budget and must be released by
+// the abort flag.  The kernel always terminates; the status word records who gave up.
+__global__ void bounded_wait_selftest_kernel(long long budget_clocks) {
+    __shared__ uint64_t bars[2];
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars[0]), 1);
+        mbar_init(smem_u32(&bars[1]), 1);
+        abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) {
+        if (warp == 0)
+            (void)mbar_wait(smem_u32(&bars[0]), 0, abort_flag, (9 << 8) | 0, budget_clocks);
+        else
+            (void)mbar_wait(smem_u32(&bars[1]), 0, abort_flag, (9 << 8) | 1);
+    }
+    __syncthreads();
+}
+
 // -------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -598,6 +623,16 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     fused_dequant_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
+}
+
+extern "C" int tcb_selftest_bounded_wait(int budget_ms, void* stream) {
+    if (budget_ms < 1 || budget_ms > 1000) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_selftest_bounded_wait: budget %d ms outside 1..1000", budget_ms);
+    int dev = 0, khz = 0;
+    TCB_CUDA_TRY(cudaGetDevice(&dev));
+    TCB_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+    bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<long long>(khz) * budget_ms);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, "tcb_selftest_bounded_wait");
 }
 
 extern "C" int tcb_fused_dequant_linear_check(void* stream) {

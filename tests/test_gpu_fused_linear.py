@@ -130,3 +130,27 @@ def test_benchmark_shape_tolerance():
         den += float((ref ** 2).sum())
     err = (num / den) ** 0.5
     assert err <= TOL and err <= EXPECTED, err
+
+
+def test_bounded_wait_times_out_cleanly_and_the_device_stays_usable():
+    """Failure detection without a fault: a wait nothing will ever satisfy runs out of its 20 ms budget,
+    the kernel returns, the status word says so, and the next GEMM works."""
+    import time
+
+    from tensorcache_b200 import _lib
+
+    L = _lib.lib()
+    dev = torch.device(DEV)
+    check_device_status()                      # clean slate
+    st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    t0 = time.time()
+    assert L.tcb_selftest_bounded_wait(20, st) == 0
+    rc = L.tcb_fused_dequant_linear_check(st)
+    assert rc == _lib.ERR_TIMEOUT and b"role 9" in L.tcb_last_error()
+    assert time.time() - t0 < 5.0
+    with pytest.raises(_lib.TcbError):
+        L.tcb_selftest_bounded_wait(20, st)
+        check_device_status()
+    assert L.tcb_fused_dequant_linear_check(st) == 0        # the word was cleared by the read
+    assert L.tcb_selftest_bounded_wait(0, st) == _lib.ERR_BAD_ARG
+    test_dequantised_operand_equals_the_decode_kernel_bits()   # the context is intact
