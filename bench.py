@@ -20,8 +20,8 @@ configuration the headline metric is quoted on.  Prints ONE JSON line.
                 device->host read of a per-batch completion word, every step.
 * ``cpu_baseline``  the C port of the reference's CPU decode (oracle/) on the host
                 cores of this box, on a bounded sample.
-* ``--impl reference``  times that CPU port alone, each step decoding a 16-sample
-                slice of the same workload, with all host threads.
+* ``--impl reference``  times that CPU port alone, each step one decode of the same
+                workload, with all host threads.
 
 Multi-GPU (torchrun, one rank per GPU): shards are independent, every rank runs
 the same per-GPU work on its own data (weak scaling), no data-path collective.
@@ -165,17 +165,16 @@ def cpu_decode_rate(numel: int, g: int, budget_s: float, max_reps: int, nthreads
 
 
 def run_reference_arm(args):
-    """CPU port of the reference decode, all host threads; step = one 16-sample slice."""
+    """CPU port of the reference decode, all host threads; step = one decode of the full workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     from oracle import amo_oracle as orc
 
     nthreads = orc.default_threads()
-    slice_shape = (16,) + SHAPE[1:]
-    numel = int(np.prod(slice_shape))
+    numel = int(np.prod(SHAPE))
     rng = np.random.default_rng(0)
-    n_sets = 8  # 8 x 16 samples = the full [128, 446, 768] workload, visited round-robin
+    n_sets = 2  # two full [128, 446, 768] workloads (271 MB together), visited alternately
     sets = []
     for _ in range(n_sets):
         q = rng.integers(0, 256, numel, dtype=np.uint8)
@@ -191,7 +190,7 @@ def run_reference_arm(args):
         orc.decompress(q, s, zp, G, nthreads=nthreads, out=out)
     dt = time.perf_counter() - t0
     value = algorithmic_bytes(numel, G) * args.steps / dt / 1e9
-    sample = f"each step decodes a [16,446,768] slice (1/8 of the workload, {numel} values) with {nthreads} threads"
+    sample = f"each step decodes the full [128,446,768] workload ({numel} values) with {nthreads} threads"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -404,13 +403,16 @@ def main():
         torch.cuda.synchronize(device)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(8):
-            d.copy_(h, non_blocking=True)
-        e1.record()
-        torch.cuda.synchronize(device)
+        best = 0.0
+        for _ in range(3):   # best of three rounds of eight copies
+            e0.record()
+            for _ in range(8):
+                d.copy_(h, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = max(best, 8 * nbytes / (e0.elapsed_time(e1) / 1e3) / 1e9)
         barrier()
-        return 8 * nbytes / (e0.elapsed_time(e1) / 1e3) / 1e9
+        return best
 
     import tensorcache_b200 as tc
     from tensorcache_b200 import _lib
