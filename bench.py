@@ -207,21 +207,26 @@ def run_reference_arm(args):
 
 # --------------------------------------------------------------------------- GPU
 
-def build_cache_shard(tc, directory: str, n_samples: int, seed: int, device) -> str:
-    """Writes one AMO-BQ G32 cache shard of [446, 768] samples with the GPU encoder."""
+def build_cache_shard(tc, directory: str, n_samples: int, seed: int, device):
+    """Writes one AMO-BQ G32 cache shard of [446, 768] samples with the GPU encoder.
+    Returns (prefix, samples per second of FeatureCacheWriter.append + close)."""
     prefix = os.path.join(directory, "feat")
-    w = tc.FeatureCacheWriter(prefix, n_samples, SHAPE[1], SHAPE[2], group_size=G, amo_bq=True, amo_mode="balanced")
     gen = torch.Generator(device=device).manual_seed(seed)
     ch = torch.exp(0.5 * torch.randn(SHAPE[2], generator=gen, device=device))
-    done = 0
-    while done < n_samples:
-        b = min(64, n_samples - done)
-        x = torch.randn((b,) + SHAPE[1:], generator=gen, device=device) * ch
-        mask = torch.rand(x.shape, generator=gen, device=device) < 0.001
-        w.append(torch.where(mask, 20 * x, x).to(torch.bfloat16))
-        done += b
+    x = torch.empty((n_samples,) + SHAPE[1:], dtype=torch.bfloat16, device=device)
+    for b in range(0, n_samples, 64):
+        n = min(64, n_samples - b)
+        v = torch.randn((n,) + SHAPE[1:], generator=gen, device=device) * ch
+        mask = torch.rand(v.shape, generator=gen, device=device) < 0.001
+        x[b:b + n] = torch.where(mask, 20 * v, v).to(torch.bfloat16)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    w = tc.FeatureCacheWriter(prefix, n_samples, SHAPE[1], SHAPE[2], group_size=G, amo_bq=True, amo_mode="balanced")
+    w.append(x)
     w.close()
-    return prefix
+    rate = n_samples / (time.perf_counter() - t0)
+    del x
+    return prefix, rate
 
 
 def scratch_dir() -> str:
@@ -488,12 +493,12 @@ def main():
     # end to end through the reader API: host memory -> GPU bf16 batches
     e2e_steps = args.e2e_steps or min(args.steps, 200)
     if args.decode_only:
-        s_contig = s_random = r_contig = r_random = float("nan")
+        s_contig = s_random = r_contig = r_random = writer_rate = float("nan")
         h2d = d2h = 0
     else:
         tmp = scratch_dir()
         try:
-            prefix = build_cache_shard(tc, tmp, 8 * SHAPE[0], 4000 + rank, device)
+            prefix, writer_rate = build_cache_shard(tc, tmp, 8 * SHAPE[0], 4000 + rank, device)
             torch.cuda.synchronize(device)
             s_contig, h2d, d2h = time_streamer(tc, prefix, device, e2e_steps, args.warmup, False, barrier)
             s_random, _, _ = time_streamer(tc, prefix, device, e2e_steps, args.warmup, True, barrier)
@@ -550,6 +555,7 @@ def main():
                 "bf16_equiv_gbs_contiguous": SHAPE[0] * e2e_steps * world * SHAPE[1] * SHAPE[2] * 2 / s_contig / 1e9,
                 "resident_contiguous_samples_per_s": SHAPE[0] * e2e_steps * world / r_contig,
                 "resident_random_samples_per_s": SHAPE[0] * e2e_steps * world / r_random,
+                "writer_samples_per_s_per_rank": writer_rate,
                 "shard_samples_per_rank": 8 * SHAPE[0], "batch_size": SHAPE[0]},
             "pcie": pcie,
             "cpu_baseline": cpu,

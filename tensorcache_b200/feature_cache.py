@@ -18,7 +18,10 @@ from typing import Optional, Union
 import numpy as np
 import torch
 
-from ._pipeline import NativePipeline, open_cache
+import ctypes
+
+from . import _lib
+from ._pipeline import NativePipeline, default_gather_threads, open_cache
 from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq
 
 
@@ -79,7 +82,7 @@ class FeatureCacheWriter:
             self.shard_prefixes = [str(self.output_prefix)]
             self.shard_sizes = [num_samples]
             self.meta_path = str(self.output_prefix) + "_meta.json"
-        self._shard_offsets = list(np.cumsum([0] + self.shard_sizes[:-1]))
+        self._shard_offsets = [int(v) for v in np.cumsum([0] + self.shard_sizes[:-1])]
         mode = "r+" if resume else "w+"
         self._maps = []
         for pref, sz in zip(self.shard_prefixes, self.shard_sizes):
@@ -164,17 +167,37 @@ class FeatureCacheWriter:
                 return si, gidx - off
         raise IndexError(f"global_idx {gidx} out of range {self.num_samples}")
 
-    def _host_staging(self, rows: int):
-        """Page-locked landing buffers for one chunk of codes (allocated once)."""
+    def _host_staging(self, which: int):
+        """Two sets of page-locked landing buffers for chunks of codes (allocated once), so that the
+        encode + device-to-host copy of one chunk overlaps the file writes of the previous one."""
         if self._staging is None:
             pin = torch.cuda.is_available()
             n = self._CHUNK
-            self._staging = (
+            self._staging = [(
                 torch.empty((n, self.seq_len, self.dim), dtype=torch.uint8, pin_memory=pin),
                 torch.empty((n, self.scales_per_sample), dtype=torch.int16, pin_memory=pin),
                 torch.empty((n, self.scales_per_sample), dtype=torch.uint8, pin_memory=pin),
-            )
-        return tuple(t[:rows] for t in self._staging)
+            ) for _ in range(2)]
+        return self._staging[which]
+
+    def _flush_chunk(self, pending):
+        """Waits for a chunk's device-to-host copies and moves its rows into the shard files
+        (multi-threaded, cache-bypassing copy; a chunk may straddle shards)."""
+        event, which, cur, start = pending
+        event.synchronize()
+        hq, hs, hz = self._host_staging(which)
+        L = _lib.lib()
+        threads = default_gather_threads()
+        pos = 0
+        while pos < cur:
+            si, li = self._shard_for_global(start + pos)
+            li = int(li)
+            take = int(min(cur - pos, self.shard_sizes[si] - li))
+            for mm, host in zip(self._maps[si], (hq, hs, hz)):
+                row_bytes = int(mm[0].nbytes)
+                _lib.check(L.tcb_gather_rows(ctypes.c_void_p(mm[li:li + take].ctypes.data),
+                                             ctypes.c_void_p(int(host.data_ptr()) + int(pos) * row_bytes), row_bytes, None, 0, take, threads))
+            pos += take
 
     def append(self, tensor_bf16: torch.Tensor):
         if tensor_bf16.ndim == 2:
@@ -184,30 +207,27 @@ class FeatureCacheWriter:
             raise ValueError(f"expected [..., {self.seq_len}, {self.dim}], got {tuple(tensor_bf16.shape)}")
         if self.current_idx + B > self.num_samples:
             raise ValueError(f"Exceeds pre-allocated {self.num_samples}: have {self.current_idx}, adding {B}")
-        done = 0
+        done, k, pending = 0, 0, None
         while done < B:
             cur = min(self._CHUNK, B - done)
             sub = tensor_bf16[done:done + cur]
             if not sub.is_cuda:
                 sub = sub.cuda(non_blocking=True)
             q, s, zp, _ = self.codec.quantize(sub)
-            hq, hs, hz = self._host_staging(cur)
-            hq.copy_(q.view(cur, self.seq_len, self.dim), non_blocking=True)
-            hs.copy_(s.view(torch.int16).view(cur, self.scales_per_sample), non_blocking=True)
-            hz.copy_(zp.view(cur, self.scales_per_sample), non_blocking=True)
-            torch.cuda.current_stream(q.device).synchronize()
-            qn, sn, zn = hq.numpy(), hs.numpy().view(np.uint16), hz.numpy()
-            pos = 0
-            while pos < cur:  # a chunk may straddle shards
-                si, li = self._shard_for_global(self.current_idx + pos)
-                take = min(cur - pos, self.shard_sizes[si] - li)
-                mq, ms, mz = self._maps[si]
-                mq[li:li + take] = qn[pos:pos + take]
-                ms[li:li + take] = sn[pos:pos + take]
-                mz[li:li + take] = zn[pos:pos + take]
-                pos += take
-            self.current_idx += cur
+            hq, hs, hz = self._host_staging(k & 1)
+            hq[:cur].copy_(q.view(cur, self.seq_len, self.dim), non_blocking=True)
+            hs[:cur].copy_(s.view(torch.int16).view(cur, self.scales_per_sample), non_blocking=True)
+            hz[:cur].copy_(zp.view(cur, self.scales_per_sample), non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(q.device))
+            if pending is not None:
+                self._flush_chunk(pending)      # overlaps the encode / copy just enqueued
+            pending = (event, k & 1, cur, self.current_idx + done)
             done += cur
+            k += 1
+        if pending is not None:
+            self._flush_chunk(pending)
+        self.current_idx += B
 
     def _meta(self, num_samples: int, prefix: str, with_bits: bool) -> dict:
         meta = {
