@@ -247,41 +247,36 @@ __device__ __forceinline__ void chunk_spill(uint8_t* sbuf, uint8_t* zbuf, int ro
 
 // One producer thread's share of a stage: row `row` of the tile, codes [32 * half, 32 * half + 32).
 // Reads the raw codes the TMA delivered (rows of 64 bytes), dequantises them and writes four
-// 16-byte chunks of bf16 into the 128-byte-swizzled A tile.  `gi` is the index, inside the
-// current scale chunk, of the group that holds the thread's first code.
-__device__ __forceinline__ void producer_convert(const uint8_t* c_stage, uint8_t* a_stage, const uint8_t* sbuf, const uint8_t* zbuf,
-                                                 int row, int half, int gi, bool two_groups, bool has_zp) {
-    // the two 16-byte reads of a thread are ordered so that a quarter warp touches 8 distinct bank groups
-    const int flip = (row >> 1) & 1;
-    const uint4* crow = reinterpret_cast<const uint4*>(c_stage + row * kBlockK + half * 32);
-    const uint4 ca = crow[flip], cb = crow[flip ^ 1];
-    const uint4 c0 = flip ? cb : ca, c1 = flip ? ca : cb;
+// 16-byte chunks of bf16 into the 128-byte-swizzled A tile.  All addresses are a per-thread base
+// (computed once, outside the main loop) plus compile-time offsets; `srow` / `zrow` point at the
+// scale / zero point of the thread's first code in the current chunk buffer.
+template <int LOG2_G, bool HAS_ZP>
+__device__ __forceinline__ void producer_convert(const uint8_t* c_thread, uint8_t* a_row, const uint32_t (&chunk_off)[4],
+                                                 const uint16_t* srow, const uint8_t* zrow) {
+    const uint4 c0 = *reinterpret_cast<const uint4*>(c_thread);
+    const uint4 c1 = *reinterpret_cast<const uint4*>(c_thread + 16);
     uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    const uint16_t* srow = reinterpret_cast<const uint16_t*>(sbuf + row * (kChunkGroups * 2));
-    const uint8_t* zrow = zbuf + row * kChunkGroups;
+    constexpr bool kTwoGroups = LOG2_G == 4;  // G = 16: the thread's 32 codes span two groups
     uint32_t sb[2], zv[2];
-    sb[0] = srow[gi];
-    sb[1] = two_groups ? uint32_t(srow[gi + 1]) : sb[0];
-    if (has_zp) {
-        zv[0] = zrow[gi];
-        zv[1] = two_groups ? uint32_t(zrow[gi + 1]) : zv[0];
+    sb[0] = srow[0];
+    sb[1] = kTwoGroups ? uint32_t(srow[1]) : sb[0];
+    if (HAS_ZP) {
+        zv[0] = zrow[0];
+        zv[1] = kTwoGroups ? uint32_t(zrow[1]) : zv[0];
     } else {  // signed codes: flip the sign bit and subtract 128
 #pragma unroll
         for (int i = 0; i < 8; ++i) words[i] ^= 0x80808080u;
         zv[0] = zv[1] = 128;
     }
-    uint8_t* row_base = a_stage + (row >> 3) * 1024 + (row & 7) * 128;
-    const int sw = row & 7;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {  // chunk j of this half: codes 8j .. 8j+7
         const int h = j >> 1;
         const float zmagic = __uint_as_float(0x4B000000u | zv[h]);  // 2^23 + zp, exact
-        const uint32_t s2 = sb[h] | (sb[h] << 16);
+        const uint32_t s2 = __byte_perm(sb[h], sb[h], 0x1010);      // the scale in both halves
         uint4 o;
         dequant_word(words[2 * j], zmagic, s2, o.x, o.y);
         dequant_word(words[2 * j + 1], zmagic, s2, o.z, o.w);
-        const int chunk = (half * 4 + j) ^ sw;
-        *reinterpret_cast<uint4*>(row_base + chunk * 16) = o;
+        *reinterpret_cast<uint4*>(a_row + chunk_off[j]) = o;
     }
 }
 
@@ -292,6 +287,7 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
 
 // -------------------------------------------------------------------- kernel
 
+template <int LOG2_G, bool HAS_ZP>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const __grid_constant__ CUtensorMap code_map, const Params p) {
     extern __shared__ uint8_t smem_raw[];
@@ -395,11 +391,21 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         // fetched one chunk ahead, across tile boundaries too.
         const int pt = threadIdx.x - kFirstProducerWarp * 32;  // 0..255
         const int row = pt >> 1, half = pt & 1;
-        const bool has_zp = p.zp != nullptr;
-        const bool two_groups = p.log2_g == 4;
-        const int log2_cs = p.log2_g - 1;                      // stages per chunk = 32 * G / 64
-        const int cs_mask = (1 << log2_cs) - 1;
-        const int chunks_per_tile = (num_kb + cs_mask) >> log2_cs;
+        constexpr int kLog2Cs = LOG2_G - 1;                    // stages per chunk = 32 * G / 64
+        constexpr int kCsMask = (1 << kLog2Cs) - 1;
+        const int chunks_per_tile = (num_kb + kCsMask) >> kLog2Cs;
+        // per-thread addresses, fixed for the whole kernel
+        const uint8_t* c_thread = smem_c + row * kBlockK + half * 32;               // + stage * kStageBytesC
+        uint8_t* a_row = smem_a + (row >> 3) * 1024 + (row & 7) * 128;               // + stage * kStageBytesA
+        uint32_t chunk_off[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) chunk_off[j] = uint32_t(((half * 4 + j) ^ (row & 7)) * 16);
+        // group (inside a chunk) of the thread's first code at stage j of the chunk:
+        // G16: 4 j + 2 half, G32: 2 j + half, G64: j
+        constexpr int kGroupsPerStage = 64 >> LOG2_G;                                // 4, 2, 1
+        const int g_half = LOG2_G == 4 ? 2 * half : (LOG2_G == 5 ? half : 0);
+        const uint8_t* s_thread = smem_s + row * (kChunkGroups * 2) + g_half * 2;   // + buf * kChunkBytesS + j * groups * 2
+        const uint8_t* z_thread = smem_z + row * kChunkGroups + g_half;             // + buf * kChunkBytesZ + j * groups
         // cursor of the chunk prefetch: (tile, chunk inside the tile)
         int pf_tile = blockIdx.x, pf_chunk = 0;
         ChunkRegs regs;
@@ -414,14 +420,21 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
             }
         };
         fetch_next_chunk();
-        uint32_t it = 0, gc = 0;  // stage counter, chunk counter
+        const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+        const int64_t total = int64_t(my_tiles) * num_kb;
+        uint32_t gc = 0;      // chunks published so far
+        uint32_t ph = 0;      // parity of the stage ring, flips once per kStages steps
+        int kb = 0;           // k-block inside the current tile
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                if ((kb & cs_mask) == 0) {
+        for (int64_t i0 = 0; ok && i0 < total; i0 += kStages, ph ^= 1) {
+#pragma unroll
+            for (int s = 0; s < kStages; ++s) {  // the stage index is a compile-time constant in here
+                if (i0 + s >= total) break;
+                const int j = kb & kCsMask;      // stage inside the chunk
+                if (j == 0) {
                     // chunk turn-over: publish the prefetched registers, start fetching the next chunk
-                    const int buf = gc & 1;
-                    chunk_spill(smem_s + buf * kChunkBytesS, smem_z + buf * kChunkBytesZ, row, half, regs);
+                    const int nb = gc & 1;
+                    chunk_spill(smem_s + nb * kChunkBytesS, smem_z + nb * kChunkBytesZ, row, half, regs);
                     fetch_next_chunk();
                     // every producer must have spilled before anyone reads the new chunk (bounded, like all waits)
                     mbar_arrive(bar(CHUNK));
@@ -429,15 +442,14 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
                     ++gc;
                 }
                 const int buf = (gc - 1) & 1;
-                const int s = it % kStages;
-                const uint32_t ph = (it / kStages) & 1;
                 if (!(ok = mbar_wait(bar(FULL_C + s), ph, abort_flag, (3 << 8) | (FULL_C + s)))) break;
-                const int j = kb & cs_mask;  // stage inside the chunk
-                const int gi = two_groups ? 4 * j + 2 * half : (p.log2_g == 5 ? 2 * j + half : j);
-                producer_convert(smem_c + s * kStageBytesC, smem_a + s * kStageBytesA, smem_s + buf * kChunkBytesS,
-                                 smem_z + buf * kChunkBytesZ, row, half, gi, two_groups, has_zp);
+                producer_convert<LOG2_G, HAS_ZP>(
+                    c_thread + s * kStageBytesC, a_row + s * kStageBytesA, chunk_off,
+                    reinterpret_cast<const uint16_t*>(s_thread + buf * kChunkBytesS + j * (kGroupsPerStage * 2)),
+                    z_thread + buf * kChunkBytesZ + j * kGroupsPerStage);
                 fence_proxy_async();  // make the generic-proxy stores visible to the tensor core
                 mbar_arrive(bar(FULL_A + s));
+                if (++kb == num_kb) kb = 0;
             }
         }
     } else {
@@ -594,12 +606,20 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled (codes) failed with %d", who, int(cr));
 
-    static bool attr_set[64] = {false};
+    // one instantiation per (group size, zero points or not): those are compile-time in the producer warps
+    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const Params);
+    static const KernelFn kernels[3][2] = {
+        {fused_dequant_gemm_kernel<4, false>, fused_dequant_gemm_kernel<4, true>},
+        {fused_dequant_gemm_kernel<5, false>, fused_dequant_gemm_kernel<5, true>},
+        {fused_dequant_gemm_kernel<6, false>, fused_dequant_gemm_kernel<6, true>}};
+    const int gi = group_size == 16 ? 0 : group_size == 32 ? 1 : 2;
+    const KernelFn kernel = kernels[gi][zp_or_null ? 1 : 0];
+    static bool attr_set[64][3][2] = {};
     int dev = 0;
     TCB_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TCB_CUDA_TRY(cudaFuncSetAttribute(fused_dequant_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-        attr_set[dev] = true;
+    if (dev >= 0 && dev < 64 && !attr_set[dev][gi][zp_or_null ? 1 : 0]) {
+        TCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+        attr_set[dev][gi][zp_or_null ? 1 : 0] = true;
     }
     Params p;
     p.q = q;
@@ -620,7 +640,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     const int64_t num_tiles = tiles_q * tiles_d;
     const int sms = tcb::sm_count();
     const int grid = int(num_tiles < sms ? num_tiles : sms);
-    fused_dequant_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
+    kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
 }
