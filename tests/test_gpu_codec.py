@@ -319,3 +319,38 @@ def test_decoder_is_cuda_graph_capturable(dev):
     graph.replay()
     torch.cuda.synchronize(dev)
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("G", [16, 32, 64])
+def test_unpadded_low_precision_input_equals_zero_padded_fp32_input(dev, dtype, G):
+    """tests/test_fused_ops.py:57-71 of the reference: the encoder reads bf16 / fp16 directly and pads
+    ragged tails itself; the result must equal encoding the zero-padded fp32 copy."""
+    import tensorcache_b200 as tc
+
+    g = torch.Generator().manual_seed(77)
+    for numel in (0, 1, 31, 32, 65, 1024):
+        x = (torch.randn(numel, generator=g) * 4).to(dtype).to(dev)
+        padded = torch.nn.functional.pad(x.float(), (0, (-numel) % G))
+        for mode in ("balanced", "quality"):
+            q1, s1, z1, _ = tc.compress(x, mode, G)
+            q2, s2, z2, _ = tc.compress(padded, mode, G)
+            assert torch.equal(q1, q2[:numel]) and torch.equal(z1, z2)
+            assert torch.equal(s1.view(torch.int16), s2.view(torch.int16))
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_nonfinite_values_reconstruct_as_zero_in_every_mode(dev, mode):
+    """tests/test_fused_ops.py:89-107 of the reference."""
+    import tensorcache_b200 as tc
+
+    g = torch.Generator().manual_seed(78)
+    x = torch.randn(4, 96, generator=g)
+    x[0, 3] = float("nan"); x[1, 40] = float("inf"); x[2, 41] = float("-inf"); x[3, :32] = float("nan")
+    for G in (16, 32):
+        q, s, zp, shape = tc.compress(x.to(torch.bfloat16).to(dev), mode, G)
+        rec = tc.decompress(q, s, shape, zp, G).float().cpu()
+        assert bool(torch.isfinite(s.float()).all()) and bool(torch.isfinite(rec).all())
+        assert bool((rec[~torch.isfinite(x)] == 0).all())
+        fin = torch.isfinite(x)
+        assert float((rec[fin] - x[fin]).abs().max()) < 0.2
