@@ -45,11 +45,13 @@ __device__ __forceinline__ float clamp255(float v) { return fminf(fmaxf(v, 0.0f)
 // exact division evaluated.  For |t~| >= 512 the two values may differ by more, but both are far
 // outside [0, 255] on the same side and clamp identically whichever path is taken.  NaN (never
 // produced for finite inputs) takes the exact path.
+constexpr float kBoundaryGuard = 0.5f - 0x1p-12f;  // distance from the nearest integer up to which the fast path is trusted
+
 __device__ __forceinline__ float quant_index(float x, float s, float r, float zp) {
     const float t = __fadd_rn(__fmul_rn(x, r), zp);
     float k = rintf(t);
     const float dist = fabsf(__fsub_rn(t, k));
-    if (!(dist <= 0.5f - 0x1p-12f)) k = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
+    if (!(dist <= kBoundaryGuard)) k = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
     return k;
 }
 
@@ -192,10 +194,24 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
             const float s = __fmul_rn(s0, tab.m[c]);
             const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
             const float rcp = __frcp_rn(s);
-            float e[VPL];
+            // Straight-line fast path for all of the lane's values (see quant_index for why it is exact
+            // away from rounding boundaries); the rare values that sit on a boundary are redone with the
+            // IEEE division afterwards, so the common case carries no per-value branch.
+            float e[VPL], kq[VPL];
+            bool doubtful = false;
 #pragma unroll
             for (int k = 0; k < VPL; ++k) {
-                const float qc = clamp255(quant_index(v[k], s, rcp, zp));
+                const float t = __fadd_rn(__fmul_rn(v[k], rcp), zp);
+                kq[k] = rintf(t);
+                doubtful |= !(fabsf(__fsub_rn(t, kq[k])) <= kBoundaryGuard);
+            }
+            if (doubtful) {
+#pragma unroll
+                for (int k = 0; k < VPL; ++k) kq[k] = quant_index(v[k], s, rcp, zp);
+            }
+#pragma unroll
+            for (int k = 0; k < VPL; ++k) {
+                const float qc = clamp255(kq[k]);
                 const float rec = __fmul_rn(__fsub_rn(qc, zp), s);
                 const float d = __fsub_rn(v[k], rec);
                 e[k] = __fmul_rn(d, d);
