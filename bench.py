@@ -50,8 +50,8 @@ G = 32
 METRIC = "amo_bq_g32_dequant_throughput"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one isolated launch of this workload
-# (profiles/decompress_v8_kernel_G32_128x446x768.md): 48.03 MB read + 35.9 MB written.
+# dram__bytes_read.sum + dram__bytes_write.sum of one isolated launch of this workload,
+# from an ncu capture of this kernel on a B200: 48.03 MB read + 35.9 MB written.
 DRAM_TRAFFIC_PER_LAUNCH = 83.9e6
 TRAFFIC_NOTE = ("bytes per launch from one ncu capture: reads 48.03 MB = algorithmic reads; of the 87.69 MB stored only "
                 "35.9 MB reach DRAM inside an isolated launch, the rest is written back from L2 afterwards")

@@ -27,8 +27,8 @@ class ShardFiles:
 
 @dataclass
 class CacheLayout:
-    """What a reader needs to know about a cache on disk (Appendix: on-disk format
-    of src/tensorcache/feature_cache.py:85-127, 134-155, 446-540)."""
+    """What a reader needs to know about a cache on disk (the file format written by
+    src/tensorcache/feature_cache.py:85-127, 134-155, 446-540 of TensorCache)."""
     meta: dict
     seq_len: int
     dim: int
