@@ -248,9 +248,9 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
 
 // ------------------------------------------------------------------ quality mode
 
-// code choice of the reference's _amo_quality_codes for one value
-__device__ __forceinline__ float quality_code(float x, float s, float rcp, float zp, float& err_out) {
-    const float r = quant_index(x, s, rcp, zp);
+// code choice of the reference's _amo_quality_codes for one value whose rounded index r = rint(x / s + zp)
+// is already known: r, r - 1 and r + 1 are tried in that order and the first smallest decoded error wins
+__device__ __forceinline__ float quality_code(float x, float s, float zp, float r, float& err_out) {
     float qv = clamp255(r);
     float d = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(qv, zp), s)));
     float err = __fmul_rn(d, d);
@@ -316,12 +316,26 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
             const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
             const float rcp = __frcp_rn(s);
-            float e[VPL];
+            // rounded indices on the straight-line fast path, boundary cases redone afterwards (as in
+            // the legacy kernel), then the three-way code choice per value
+            float e[VPL], r[VPL];
+            bool doubtful = false;
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
-                float err;
-                (void)quality_code(v[i], s, rcp, zp, err);
-                e[i] = ((finmask >> i) & 1u) ? err : 0.0f;
+                const float t = __fadd_rn(__fmul_rn(v[i], rcp), zp);
+                r[i] = rintf(t);
+                doubtful |= !(fabsf(__fsub_rn(t, r[i])) <= kBoundaryGuard);
+            }
+            if (doubtful) {
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) r[i] = quant_index(v[i], s, rcp, zp);
+            }
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) (void)quality_code(v[i], s, zp, r[i], e[i]);
+            if (finmask != (1u << VPL) - 1u) {  // rare: positions that held NaN / Inf do not count
+#pragma unroll
+                for (int i = 0; i < VPL; ++i)
+                    if (!((finmask >> i) & 1u)) e[i] = 0.0f;
             }
             const float tot = quad_sum<G>(e, j, lane, qmask);
             if (k == 0 || tot < best_err) {
@@ -333,10 +347,11 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
 
         uint8_t codes[VPL];
         const uint8_t zp8 = uint8_t(best_zp);
+        const float best_rcp = __frcp_rn(best_s);
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             float err;
-            const float qf = quality_code(v[i], best_s, __frcp_rn(best_s), best_zp, err);
+            const float qf = quality_code(v[i], best_s, best_zp, quant_index(v[i], best_s, best_rcp, best_zp), err);
             codes[i] = ((finmask >> i) & 1u) ? uint8_t(qf) : zp8;
         }
         store_codes<G>(q, numel, base, j, out_aligned, codes);
