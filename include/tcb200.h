@@ -64,9 +64,10 @@ TCB_API const char* tcb_last_error(void);
  *   scales  [ceil(numel / G)]  bf16 bit patterns
  *   zp      [ceil(numel / G)]  uint8 zero points
  *   out     [numel]            bf16 bit patterns (may be a caller-owned out_buffer)
- * G must be 16, 32 or 64.  numel may be 0 and need not be a multiple of G.  The
- * fast path needs q and out 16-byte aligned; other alignments take a slower
- * element-wise kernel with identical results.
+ * G must be 8, 16, 24, 32, 48, 64 or 128 (the reference's CPU path takes any G;
+ * these are the sizes its tests and presets use).  numel may be 0 and need not be
+ * a multiple of G.  The fast path needs q and out 16-byte aligned; other
+ * alignments take a slower element-wise kernel with identical results.
  */
 TCB_API int tcb_decompress_amo(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out,
                        int64_t numel, int group_size, void* stream);
@@ -107,7 +108,8 @@ TCB_API int tcb_decompress_amo_host_noalloc(const uint8_t* q_host, const uint16_
  *                the values of torch.linspace(lo, hi, n_cand) computed on the CPU
  *                (codec.py:852); they are passed by value to the kernel
  *   q, scales, zp  outputs laid out as for tcb_decompress_amo
- * G must be 16, 32 or 64; the last group is zero-padded as the reference pads.
+ * G must be 8, 16, 24, 32, 48, 64 or 128; the last group is zero-padded as the
+ * reference pads.
  */
 TCB_API int tcb_compress_amo(const void* x, int dtype, int64_t numel, int group_size, const float* multipliers,
                      int n_cand, uint8_t* q, uint16_t* scales, uint8_t* zp, void* stream);
@@ -120,6 +122,31 @@ TCB_API int tcb_compress_amo(const void* x, int dtype, int64_t numel, int group_
  */
 TCB_API int tcb_compress_amo_quality(const void* x, int dtype, int64_t numel, int group_size, uint8_t* q,
                              uint16_t* scales, uint8_t* zp, void* stream);
+
+/*
+ * Symmetric int8 codec (signed codes, one bf16 scale per group, no zero point).
+ * n_cand == 0 replaces quantize_int8_g32 (src/tensorcache/codec.py:530-565):
+ * scale = bf16(max|x| / 127), q = clamp(rne(x / scale), -128, 127).
+ * n_cand > 0 replaces quantize_int8_adaptive (src/tensorcache/codec.py:568-620):
+ * the scale is searched over (max|x| / 127) * multipliers[c], the host values of
+ * torch.linspace(0.90, 1.05, n_cand), scored by squared error, first minimum wins.
+ * Both reproduce the CPU path bit for bit; non-finite inputs become code 0.
+ * These are also the codes FusedDequantLinear takes with zp == NULL.
+ *   q       [numel]            int8 codes          scales  [ceil(numel / G)] bf16 bits
+ * Group sizes as for tcb_compress_amo; 0 <= n_cand <= 64.
+ */
+TCB_API int tcb_compress_sym(const void* x, int dtype, int64_t numel, int group_size, const float* multipliers,
+                             int n_cand, int8_t* q, uint16_t* scales, void* stream);
+
+/*
+ * Symmetric decode: out[i] = bf16( int8(q[i]) * scale[i / G] ), bit-exact (the
+ * product is exact in fp32).  Replaces dequantize_int8_g32
+ * (src/tensorcache/codec.py:623-697; Triton kernel codec.py:214-231) and
+ * utils.decompress with zero_points=None (src/tensorcache/utils.py:150-152).
+ * Sizes, alignment and group sizes as for tcb_decompress_amo.
+ */
+TCB_API int tcb_decompress_sym(const int8_t* q, const uint16_t* scales, uint16_t* out, int64_t numel, int group_size,
+                               void* stream);
 
 /*
  * Fused dequantise + GEMM on the tcgen05 tensor cores:
@@ -186,7 +213,9 @@ typedef struct tcb_streamer_desc {
     int n_shards;                  /* >= 1; samples are numbered shard after shard           */
     const void* const* q_bases;    /* [n_shards] mapped [size, values_per_sample] codes      */
     const void* const* s_bases;    /* [n_shards] mapped [size, groups_per_sample] bf16 bits  */
-    const void* const* zp_bases;   /* [n_shards] mapped [size, groups_per_sample] zero points */
+    const void* const* zp_bases;   /* [n_shards] mapped [size, groups_per_sample] zero points;
+                                      NULL for a cache of the symmetric codec (int8 codes, no
+                                      zero points): pinned_zp / dev_zp are then unused and may be NULL */
     const int64_t* shard_sizes;    /* [n_shards] samples per shard                           */
     int64_t values_per_sample;     /* seq_len * dim, a multiple of group_size                */
     int64_t groups_per_sample;     /* values_per_sample / group_size                         */

@@ -18,6 +18,9 @@
  *   quality mode     src/tensorcache/codec.py:721-771  (_amo_quality_codes,
  *                                                       _quantize_amo_quality_torch)
  *   decode           src/tensorcache/codec.py:953-966  (dequantize_int8_amo_bq)
+ *   symmetric codec  src/tensorcache/codec.py:530-565  (quantize_int8_g32),
+ *                    src/tensorcache/codec.py:568-620  (quantize_int8_adaptive),
+ *                    src/tensorcache/codec.py:685-695  (dequantize_int8_g32, CPU branch)
  *
  * Arithmetic rules that make the restatement bit-exact:
  *   - every operation is a separate IEEE-754 binary32 operation (compile with
@@ -261,6 +264,59 @@ static void encode_group_quality(const float* xin, int G, uint8_t* q_out, uint16
     *zp_out = (uint8_t)best_zp;
 }
 
+static inline float clamp_i8(float v) {
+    if (v != v) return v;
+    if (v < -128.0f) v = -128.0f;
+    if (v > 127.0f) v = 127.0f;
+    return v;
+}
+
+/* codec.py:530-565 (ncand == 0) and codec.py:568-620 (ncand > 0, the "adaptive"
+ * scale search), one group.  Signed codes, one bf16 scale, no zero point.  The
+ * adaptive search scores the candidates on the RAW values (a NaN or Inf in the
+ * group makes every error NaN or Inf and candidate 0 wins), then quantises the
+ * cleaned values with the bf16-rounded winner. */
+static void encode_group_sym(const float* xin, int G, const float* mult, int ncand,
+                             int8_t* q_out, uint16_t* s_out) {
+    float x[TCB_ORACLE_MAX_G];
+    unsigned char fin[TCB_ORACLE_MAX_G];
+    float e[TCB_ORACLE_MAX_G];
+    float bmax = 0.0f;
+    for (int i = 0; i < G; ++i) {
+        fin[i] = isfinite(xin[i]) ? 1 : 0;
+        x[i] = fin[i] ? xin[i] : 0.0f;
+        float a = fabsf(x[i]);
+        if (a > bmax) bmax = a;
+    }
+    if (bmax < 1e-8f) bmax = 1e-8f;
+    float s0 = bmax / 127.0f;
+    float best_s = s0;
+    if (ncand > 0) {
+        float best_err = 0.0f;
+        for (int c = 0; c < ncand; ++c) {
+            float s = s0 * mult[c];
+            for (int i = 0; i < G; ++i) {
+                float qc = clamp_i8(nearbyintf(xin[i] / s));
+                float rec = qc * s;
+                float d = xin[i] - rec;
+                e[i] = d * d;
+            }
+            float err = sum_group(e, G);
+            if (c == 0 || better_than(err, best_err)) {
+                best_err = err;
+                best_s = s;
+            }
+        }
+    }
+    uint16_t sb = f32_to_bf16_bits(best_s);
+    float sf = bf16_bits_to_f32(sb);
+    for (int i = 0; i < G; ++i) {
+        float qf = clamp_i8(nearbyintf(x[i] / sf));
+        q_out[i] = fin[i] ? (int8_t)qf : 0;
+    }
+    *s_out = sb;
+}
+
 /* -------------------------------------------------------------- threading */
 
 typedef void (*range_fn)(void* ctx, int64_t lo, int64_t hi);
@@ -389,6 +445,60 @@ int tcb_oracle_compress_quality(const void* x, int dtype, int64_t numel, int gro
     enc_ctx c = {x, dtype, numel, group_size, NULL, 0, q, scales, zp};
     parallel_for(numel, group_size, nthreads, enc_range, &c);
     return 0;
+}
+
+typedef struct {
+    const void* x;
+    int dtype;
+    int64_t numel;
+    int G;
+    const float* mult;
+    int ncand;
+    int8_t* q;
+    uint16_t* s;
+} sym_ctx;
+
+static void sym_enc_range(void* p, int64_t lo, int64_t hi) {
+    sym_ctx* c = (sym_ctx*)p;
+    int G = c->G;
+    float xin[TCB_ORACLE_MAX_G];
+    int8_t qtmp[TCB_ORACLE_MAX_G];
+    for (int64_t base = lo; base < hi; base += G) {
+        int64_t n_here = c->numel - base < G ? c->numel - base : G;
+        for (int i = 0; i < G; ++i)
+            xin[i] = i < n_here ? load_as_f32(c->x, c->dtype, base + i) : 0.0f;
+        encode_group_sym(xin, G, c->mult, c->ncand, qtmp, &c->s[base / G]);
+        memcpy(c->q + base, qtmp, (size_t)n_here);
+    }
+}
+
+/* Symmetric int8 codec: n_cand == 0 is quantize_int8_g32, n_cand > 0 is
+ * quantize_int8_adaptive with the given multipliers (torch.linspace(0.90, 1.05, n)). */
+int tcb_oracle_compress_sym(const void* x, int dtype, int64_t numel, int group_size,
+                            const float* multipliers, int n_cand, int8_t* q, uint16_t* scales,
+                            int nthreads) {
+    if (group_size <= 0 || group_size > TCB_ORACLE_MAX_G || n_cand < 0) return -1;
+    sym_ctx c = {x, dtype, numel, group_size, multipliers, n_cand, q, scales};
+    parallel_for(numel, group_size, nthreads, sym_enc_range, &c);
+    return 0;
+}
+
+static void sym_dec_range(void* p, int64_t lo, int64_t hi) {
+    dec_ctx* c = (dec_ctx*)p;
+    int G = c->G;
+    for (int64_t base = lo; base < hi; base += G) {
+        float s = bf16_bits_to_f32(c->s[base / G]);
+        int64_t end = base + G < hi ? base + G : hi;
+        for (int64_t i = base; i < end; ++i)
+            c->out[i] = f32_to_bf16_bits((float)(int8_t)c->q[i] * s); /* codec.py:691-694 */
+    }
+}
+
+/* out[i] = bf16(f32(int8 q[i]) * f32(scale[i / G])) */
+void tcb_oracle_decompress_sym(const int8_t* q, const uint16_t* scales, uint16_t* out,
+                               int64_t numel, int group_size, int nthreads) {
+    dec_ctx c = {(const uint8_t*)q, scales, NULL, out, numel, group_size};
+    parallel_for(numel, group_size, nthreads, sym_dec_range, &c);
 }
 
 typedef struct {

@@ -55,6 +55,10 @@ def lib() -> ctypes.CDLL:
         L.tcb_oracle_compress_quality.restype = i32
         L.tcb_oracle_dequant_matmul.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32]
         L.tcb_oracle_dequant_matmul.restype = None
+        L.tcb_oracle_compress_sym.argtypes = [vp, i32, i64, i32, vp, i32, vp, vp, i32]
+        L.tcb_oracle_compress_sym.restype = i32
+        L.tcb_oracle_decompress_sym.argtypes = [vp, vp, vp, i64, i32, i32]
+        L.tcb_oracle_decompress_sym.restype = None
         L.tcb_oracle_sum_group.argtypes = [vp, i32]
         L.tcb_oracle_sum_group.restype = ctypes.c_float
         _lib = L
@@ -122,6 +126,32 @@ def decompress(q: np.ndarray, scales: np.ndarray, zp: np.ndarray, group_size: in
     if out is None:
         out = np.empty(q.size, np.uint16)
     lib().tcb_oracle_decompress(_ptr(q), _ptr(scales), _ptr(zp), _ptr(out), q.size, group_size, nthreads)
+    return out
+
+
+def compress_sym(x: np.ndarray, group_size: int = 32, adaptive: bool = False, num_candidates: int = 31,
+                 nthreads: int = 1):
+    """(q int8 [numel], scales uint16 [ceil(numel/G)]) of the symmetric codec; ``adaptive`` runs the
+    reference's scale search over torch.linspace(0.90, 1.05, num_candidates)."""
+    xin, dt = _as_input(x)
+    numel = xin.size
+    q = np.empty(numel, np.int8)
+    s = np.empty((numel + group_size - 1) // group_size, np.uint16)
+    m = linspace_multipliers(0.90, 1.05, num_candidates) if adaptive else None
+    rc = lib().tcb_oracle_compress_sym(_ptr(xin), dt, numel, group_size, _ptr(m), num_candidates if adaptive else 0,
+                                       _ptr(q), _ptr(s), nthreads)
+    if rc != 0:
+        raise ValueError("oracle: unsupported group size / candidate count")
+    return q, s
+
+
+def decompress_sym(q: np.ndarray, scales: np.ndarray, group_size: int = 32, nthreads: int = 1) -> np.ndarray:
+    """bf16 bit patterns (uint16) of int8 q * scale, flat."""
+    q = np.ascontiguousarray(q).reshape(-1)
+    scales = np.ascontiguousarray(scales).reshape(-1)
+    assert q.dtype == np.int8 and scales.dtype == np.uint16
+    out = np.empty(q.size, np.uint16)
+    lib().tcb_oracle_decompress_sym(_ptr(q), _ptr(scales), _ptr(out), q.size, group_size, nthreads)
     return out
 
 

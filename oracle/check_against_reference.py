@@ -9,7 +9,8 @@ it only runs where the reference is mounted; the committed fixtures under
 Compares q / scale bits / zero points of ``tc.compress`` (CPU tensors) and the
 bf16 bits of ``tc.decompress`` with the oracle, over the BASELINE-style synthetic
 tensors, the edge cases of the reference tests (empty, 1, 31, 32, 33, 65, 1024,
-1027 values; NaN / Inf; constant groups) and random group sizes.
+1027 values; NaN / Inf; constant groups) and random group sizes; likewise the
+symmetric codec (``quantize_int8_g32`` / ``quantize_int8_adaptive`` / ``dequantize_int8_g32``).
 """
 from __future__ import annotations
 
@@ -84,6 +85,27 @@ def compare(tc, x: torch.Tensor, mode, G, label, nthreads, **kw):
     return ok
 
 
+def compare_sym(tc, x: torch.Tensor, adaptive: bool, G, label, nthreads):
+    """quantize_int8_g32 / quantize_int8_adaptive and dequantize_int8_g32 against the oracle."""
+    from tensorcache.codec import dequantize_int8_g32, quantize_int8_adaptive, quantize_int8_g32
+
+    t0 = time.time()
+    q, s, _ = (quantize_int8_adaptive if adaptive else quantize_int8_g32)(x, G)
+    t1 = time.time()
+    oq, os_ = orc.compress_sym(to_oracle_input(x), G, adaptive, nthreads=nthreads)
+    t2 = time.time()
+    dq = int((q.numpy().reshape(-1) != oq).sum())
+    ds = int((bits(s) != os_).sum()) if s.numel() else 0
+    dr = 0
+    if q.numel():
+        rec = dequantize_int8_g32(q, s, tuple(x.shape), G)
+        dr = int((bits(rec) != orc.decompress_sym(oq, os_, G, nthreads=nthreads)).sum())
+    ok = dq == 0 and ds == 0 and dr == 0
+    print(f"{'OK  ' if ok else 'FAIL'} {label:46s} numel={x.numel():>10d} q!={dq} s!={ds} rec!={dr}"
+          f"  ref {t1 - t0:6.2f}s oracle {t2 - t1:6.2f}s", flush=True)
+    return ok
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="directory of the TensorCache checkout (contains src/)")
@@ -135,6 +157,31 @@ def main():
         xx = (torch.randn(32 * 2000, generator=g) * scale).to(torch.float32)
         for mode in ("balanced", "quality"):
             ok &= compare(tc, xx, mode, 32, f"magnitude {scale:g} {mode}", nt)
+
+    # symmetric codec (plain and with the adaptive scale search)
+    g = torch.Generator().manual_seed(9)
+    for numel in (0, 1, 31, 32, 33, 65, 1027):
+        xx = (torch.randn(numel, generator=g) * 3).to(torch.bfloat16)
+        for adaptive in (False, True):
+            for G in (16, 32, 64):
+                ok &= compare_sym(tc, xx, adaptive, G, f"sym edge numel={numel} adaptive={adaptive} G{G}", 1)
+    xn = torch.randn(4096, generator=g)
+    xn[5] = float("nan"); xn[40] = float("inf"); xn[41] = float("-inf"); xn[64:96] = float("nan")
+    xn[128:160] = 3.0; xn[160:192] = -3.0; xn[192:224] = 0.0; xn[224:256] = 1e30; xn[300] = -1e38; xn[301] = 3e38
+    for dt in (torch.bfloat16, torch.float32, torch.float16):
+        for adaptive in (False, True):
+            for G in (16, 32, 64):
+                ok &= compare_sym(tc, xn.to(dt), adaptive, G, f"sym nonfinite/const {str(dt)[6:]} adaptive={adaptive} G{G}", 1)
+    for G in (8, 24, 48, 128):
+        for adaptive in (False, True):
+            ok &= compare_sym(tc, x, adaptive, G, f"sym odd G adaptive={adaptive} G{G}", nt)
+    for scale in (1e-30, 1e-38, 1e-41, 1e30, 1e37):
+        xx = (torch.randn(32 * 2000, generator=g) * scale).to(torch.float32)
+        for adaptive in (False, True):
+            ok &= compare_sym(tc, xx, adaptive, 32, f"sym magnitude {scale:g} adaptive={adaptive}", nt)
+    for adaptive in (False, True):
+        ok &= compare_sym(tc, config0_style(0, (4, 446, 768)), adaptive, 32, f"sym config0[:4] adaptive={adaptive}", nt)
+        ok &= compare_sym(tc, student_t_style(2, (2, 1024, 1024)), adaptive, 32, f"sym config2-slice adaptive={adaptive}", nt)
 
     # BASELINE-style tensors
     x0 = config0_style(0, (16, 446, 768))

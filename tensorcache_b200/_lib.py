@@ -55,6 +55,8 @@ SIGNATURES = {
     "tcb_decompress_amo_host_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_compress_amo": (_i32, [_vp, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
     "tcb_compress_amo_quality": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp]),
+    "tcb_compress_sym": (_i32, [_vp, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp]),
+    "tcb_decompress_sym": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_fused_dequant_linear": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tcb_fused_dequant_linear_check": (_i32, [_vp]),
     "tcb_selftest_bounded_wait": (_i32, [_i32, _vp]),

@@ -17,10 +17,11 @@ from . import _lib
 
 @dataclass
 class ShardFiles:
-    """One file set ``<prefix>_int8.bin / _scales.bin / _zp.bin`` opened read-only."""
+    """One file set ``<prefix>_int8.bin / _scales.bin / _zp.bin`` opened read-only.  A cache of the
+    symmetric codec (``amo_bq`` false) holds int8 codes and has no ``_zp.bin``; ``zp`` stays None."""
     prefix: str
     num_samples: int
-    q: Optional[np.memmap] = None      # uint8 [n, seq, dim]
+    q: Optional[np.memmap] = None      # uint8 (AMO-BQ) or int8 (symmetric) [n, seq, dim]
     s: Optional[np.memmap] = None      # uint16 [n, groups] (bf16 bit patterns)
     zp: Optional[np.memmap] = None     # uint8 [n, groups]
 
@@ -83,12 +84,11 @@ class CacheLayout:
 
 
 def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq: bool, private: bool = False) -> ShardFiles:
-    if not amo_bq:
-        raise NotImplementedError("this cache was written with the symmetric INT8 codec; only AMO-BQ caches "
-                                  "(amo_bq=True) are readable on the B200 path")
     sh = ShardFiles(prefix, n)
     if n > 0:
-        expect = {"_int8.bin": n * seq_len * dim, "_scales.bin": n * groups * 2, "_zp.bin": n * groups}
+        expect = {"_int8.bin": n * seq_len * dim, "_scales.bin": n * groups * 2}
+        if amo_bq:
+            expect["_zp.bin"] = n * groups
         for suffix, nbytes in expect.items():
             path = prefix + suffix
             if not os.path.exists(path):
@@ -99,9 +99,10 @@ def _open_shard(prefix: str, n: int, seq_len: int, dim: int, groups: int, amo_bq
         # "c" = private copy-on-write mapping: never written here, but the only kind of file mapping
         # the CUDA driver agrees to page-lock (resident-shard mode of the readers)
         mode = "c" if private else "r"
-        sh.q = np.memmap(prefix + "_int8.bin", dtype=np.uint8, mode=mode, shape=(n, seq_len, dim))
+        sh.q = np.memmap(prefix + "_int8.bin", dtype=np.uint8 if amo_bq else np.int8, mode=mode, shape=(n, seq_len, dim))
         sh.s = np.memmap(prefix + "_scales.bin", dtype=np.uint16, mode=mode, shape=(n, groups))
-        sh.zp = np.memmap(prefix + "_zp.bin", dtype=np.uint8, mode=mode, shape=(n, groups))
+        if amo_bq:
+            sh.zp = np.memmap(prefix + "_zp.bin", dtype=np.uint8, mode=mode, shape=(n, groups))
     return sh
 
 
@@ -215,6 +216,8 @@ class NativePipeline:
                         if sh.num_samples == 0:
                             continue
                         for arr in (sh.q, sh.s, sh.zp):
+                            if arr is None:
+                                continue
                             nbytes = (arr.nbytes + 4095) // 4096 * 4096   # the mapping covers whole pages
                             _lib.check(_lib.lib().tcb_pin_host_range(ctypes.c_void_p(arr.ctypes.data), nbytes))
                             self._pinned_ranges.append(arr.ctypes.data)
@@ -222,16 +225,20 @@ class NativePipeline:
                     self._unpin()
                     raise
         # the staging copy of the codes is not needed when the copy engine reads the shard itself
+        amo = layout.amo_bq
+        qdt = torch.uint8 if amo else torch.int8
         self.pinned_q = [] if self.pin_shards else [
-            torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
+            torch.empty((B, layout.seq_len, layout.dim), dtype=qdt, pin_memory=True) for _ in range(n_slots)]
         self.pinned_s = [torch.empty((B, gps), dtype=torch.bfloat16, pin_memory=True) for _ in range(n_slots)]
-        self.pinned_zp = [torch.empty((B, gps), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)]
-        self.dev_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.uint8, device=device) for _ in range(n_slots)]
+        self.pinned_zp = [torch.empty((B, gps), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)] if amo else None
+        self.dev_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=qdt, device=device) for _ in range(n_slots)]
         self.dev_s = [torch.empty((B, gps), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
-        self.dev_zp = [torch.empty((B, gps), dtype=torch.uint8, device=device) for _ in range(n_slots)]
+        self.dev_zp = [torch.empty((B, gps), dtype=torch.uint8, device=device) for _ in range(n_slots)] if amo else None
         self.dev_out = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
 
         def table(tensors):
+            if tensors is None:
+                return None
             if not tensors:
                 return (ctypes.c_void_p * n_slots)(*([None] * n_slots))
             return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
@@ -241,7 +248,7 @@ class NativePipeline:
                 *[(getattr(sh, name).ctypes.data if sh.num_samples > 0 else 0) for sh in layout.shards])
 
         self._tables = [table(t) for t in (self.pinned_q, self.pinned_s, self.pinned_zp, self.dev_q, self.dev_s, self.dev_zp, self.dev_out)]
-        self._bases = [base_table("q"), base_table("s"), base_table("zp")]
+        self._bases = [base_table("q"), base_table("s"), base_table("zp") if amo else None]
         self._sizes = (ctypes.c_int64 * len(layout.shards))(*layout.shard_sizes)
         d = _lib.StreamerDesc()
         d.n_shards = len(layout.shards)

@@ -1,7 +1,9 @@
 """AMO-BQ codec on the B200 kernels, with the reference's Python signatures.
 
 Mirrors ``src/tensorcache/codec.py:700-1041`` of TensorCache (``AMO_BQ_PRESETS``,
-``quantize_int8_amo_bq``, ``dequantize_int8_amo_bq``, ``BlockwiseInt8Codec``).
+``quantize_int8_amo_bq``, ``dequantize_int8_amo_bq``, ``BlockwiseInt8Codec``) and the
+symmetric codec next to it (``quantize_int8_g32``, ``quantize_int8_adaptive``,
+``dequantize_int8_g32``, ``codec.py:530-697``).
 All arithmetic runs in the CUDA library; CPU tensors are accepted for drop-in
 compatibility by staging them through the current CUDA device (the results are
 bit-identical to the reference's CPU path, so callers cannot tell), and the
@@ -28,7 +30,7 @@ AMO_BQ_PRESETS = {
     "quality": (64, 0.85, 1.10, "bf16-grid search scored on decoded values"),
 }
 
-SUPPORTED_GROUP_SIZES = (16, 32, 64)
+SUPPORTED_GROUP_SIZES = (8, 16, 24, 32, 48, 64, 128)
 _DTYPES = {torch.bfloat16: _lib.DT_BF16, torch.float16: _lib.DT_F16, torch.float32: _lib.DT_F32}
 
 
@@ -156,11 +158,81 @@ def dequantize_int8_amo_bq(
     return out_buffer
 
 
+def _quantize_sym(x: torch.Tensor, group_size: int, num_candidates: int):
+    _check_group_size(group_size)
+    if x.dtype not in _DTYPES:
+        x = x.float()
+    dev = _compute_device(x)
+    orig_shape = x.shape
+    numel = x.numel()
+    ngroups = (numel + group_size - 1) // group_size
+    with torch.cuda.device(dev):
+        xd = x.reshape(-1).contiguous() if x.is_cuda else x.reshape(-1).contiguous().to(dev)
+        q = torch.empty(numel, dtype=torch.int8, device=dev)
+        s = torch.empty(ngroups, dtype=torch.bfloat16, device=dev)
+        if numel:
+            stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            if num_candidates:
+                if not 1 <= int(num_candidates) <= 64:
+                    raise ValueError(f"num_candidates {num_candidates} outside 1..64")
+                m = _multipliers(0.90, 1.05, int(num_candidates))
+                mp = ctypes.c_void_p(m.ctypes.data)
+            else:
+                mp = ctypes.c_void_p(0)
+            _lib.check(_lib.lib().tcb_compress_sym(_ptr(xd), _DTYPES[xd.dtype], numel, group_size, mp, int(num_candidates),
+                                                   _ptr(q), _ptr(s), stream))
+    if not x.is_cuda:
+        q, s = q.cpu(), s.cpu()
+    return q, s, orig_shape
+
+
+def quantize_int8_g32(x: torch.Tensor, group_size: int = 32):
+    """Symmetric block-wise int8: ``(q int8 [numel], scales bf16 [ceil(numel/G)], orig_shape)``.
+
+    Contract and bits of the reference's CPU path (codec.py:530-565): scale = bf16(max|x| / 127),
+    q = clamp(round(x / scale), -128, 127), non-finite values become 0.
+    """
+    return _quantize_sym(x, group_size, 0)
+
+
+def quantize_int8_adaptive(x: torch.Tensor, group_size: int = 32, num_candidates: int = 31):
+    """Symmetric int8 with the reference's least-squares scale search over 0.90-1.05 (codec.py:568-620)."""
+    return _quantize_sym(x, group_size, num_candidates)
+
+
+def dequantize_int8_g32(q_int8: torch.Tensor, scales: torch.Tensor, orig_shape: Tuple[int, ...], group_size: int = 32,
+                        out_buffer: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Symmetric decode ``rec = q * scale`` -> bf16; contract of codec.py:623-697."""
+    _check_group_size(group_size)
+    numel = q_int8.numel()
+    ngroups = (numel + group_size - 1) // group_size
+    if scales.numel() < ngroups:
+        raise ValueError(f"need {ngroups} scales for {numel} values at G={group_size}, got {scales.numel()}")
+    if q_int8.dtype != torch.int8 or scales.dtype != torch.bfloat16:
+        raise ValueError("symmetric decode takes int8 codes and bf16 scales")
+    dev = _compute_device(q_int8)
+    if out_buffer is None:
+        out_buffer = torch.empty(orig_shape, dtype=torch.bfloat16, device=q_int8.device)
+    if out_buffer.numel() != numel or out_buffer.dtype != torch.bfloat16:
+        raise ValueError("out_buffer must be a bf16 tensor with as many elements as q")
+    if numel == 0:
+        return out_buffer
+    with torch.cuda.device(dev):
+        qd = q_int8.contiguous().to(dev)
+        sd = scales.contiguous().to(dev)
+        direct = out_buffer.is_cuda and out_buffer.device == dev and out_buffer.is_contiguous()
+        od = out_buffer if direct else torch.empty(numel, dtype=torch.bfloat16, device=dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(_lib.lib().tcb_decompress_sym(_ptr(qd), _ptr(sd), _ptr(od), numel, group_size, stream))
+        if not direct:
+            out_buffer.copy_(od.view(out_buffer.shape))
+    return out_buffer
+
+
 class BlockwiseInt8Codec:
     """Configuration holder with ``quantize`` / ``dequantize``; mirrors codec.py:969-1041.
 
-    Only the AMO-BQ mode is implemented on the B200 path; the symmetric and
-    adaptive codecs of the reference are outside it and raise NotImplementedError.
+    Default is the symmetric codec, ``adaptive=True`` its scale search, ``amo_bq=True`` AMO-BQ.
     """
 
     def __init__(self, group_size: int = 32, adaptive: bool = False, amo_bq: bool = False,
@@ -189,12 +261,14 @@ class BlockwiseInt8Codec:
         return f"BlockwiseInt8Codec(G={self.group_size}, sym 1:{2 / (1 + 2 / self.group_size):.2f}x)"
 
     def quantize(self, x: torch.Tensor):
-        if not self.amo_bq:
-            raise NotImplementedError("only amo_bq=True is implemented on the B200 path (symmetric / adaptive codecs are not)")
-        return quantize_int8_amo_bq(x, group_size=self.group_size, num_candidates=self.amo_candidates,
-                                    lo=self.amo_lo, hi=self.amo_hi, mode=self.amo_mode)
+        if self.amo_bq:
+            return quantize_int8_amo_bq(x, group_size=self.group_size, num_candidates=self.amo_candidates,
+                                        lo=self.amo_lo, hi=self.amo_hi, mode=self.amo_mode)
+        if self.adaptive:
+            return quantize_int8_adaptive(x, group_size=self.group_size)
+        return quantize_int8_g32(x, group_size=self.group_size)
 
     def dequantize(self, q_int8, scales, orig_shape, zero_points=None, out_buffer=None):
         if zero_points is None:
-            raise NotImplementedError("symmetric decode (no zero points) is not implemented on the B200 path")
+            return dequantize_int8_g32(q_int8, scales, orig_shape, group_size=self.group_size, out_buffer=out_buffer)
         return dequantize_int8_amo_bq(q_int8, scales, zero_points, orig_shape, group_size=self.group_size, out_buffer=out_buffer)

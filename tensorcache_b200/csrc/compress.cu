@@ -105,20 +105,22 @@ __device__ __forceinline__ void load_lane(const T* __restrict__ x, int64_t numel
 // term of element 8k + 2j + a.  Returns the total on every lane of the quad.
 template <int G>
 __device__ __forceinline__ float quad_sum(const float (&e)[G / 4], int j, int lane, uint32_t qmask) {
+    // Column totals in ATen's order: complete runs of four 8-wide vectors feed four accumulators
+    // (vector v of a run goes to accumulator v % 4), left-over vectors go to accumulator 0, and the
+    // accumulators are combined ((a0 + a1) + a2) + a3.  All indices are compile-time constants.
+    constexpr int NVEC = G / 8;
+    constexpr int FULL = (NVEC / 4) * 4;
     float col[2];
 #pragma unroll
     for (int a = 0; a < 2; ++a) {
-        if (G == 16) {
-            col[a] = __fadd_rn(e[a], e[2 + a]);
-        } else if (G == 32) {
-            col[a] = __fadd_rn(__fadd_rn(__fadd_rn(e[a], e[2 + a]), e[4 + a]), e[6 + a]);
-        } else {  // 64: accumulator i gets vectors i and 4 + i
-            float a0 = __fadd_rn(e[a], e[8 + a]);
-            float a1 = __fadd_rn(e[2 + a], e[10 + a]);
-            float a2 = __fadd_rn(e[4 + a], e[12 + a]);
-            float a3 = __fadd_rn(e[6 + a], e[14 + a]);
-            col[a] = __fadd_rn(__fadd_rn(__fadd_rn(a0, a1), a2), a3);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int vI = 0; vI < NVEC; ++vI) {
+            const int t = vI < FULL ? (vI & 3) : 0;
+            const bool first = vI < FULL ? vI < 4 : (FULL == 0 && vI == 0);
+            acc[t] = first ? e[2 * vI + a] : __fadd_rn(acc[t], e[2 * vI + a]);
         }
+        col[a] = FULL > 0 ? __fadd_rn(__fadd_rn(__fadd_rn(acc[0], acc[1]), acc[2]), acc[3]) : acc[0];
     }
     // lane totals L0..L7 are added left to right: lane 0 starts, lanes 1..3 continue
     const int q0 = lane & ~3;
@@ -164,6 +166,7 @@ __global__ void __launch_bounds__(kThreads)
 compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                        uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned, bool out_aligned) {
     constexpr int VPL = G / 4;
+    constexpr uint32_t kAllFinite = VPL >= 32 ? 0xffffffffu : (1u << (VPL & 31)) - 1u;
     const int lane = threadIdx.x & 31;
     const int j = lane & 3;
     const uint32_t qmask = 0xFu << (lane & ~3);
@@ -216,7 +219,7 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
                 const float d = __fsub_rn(v[k], rec);
                 e[k] = __fmul_rn(d, d);
             }
-            if (finmask != (1u << VPL) - 1u) {  // rare: positions that held NaN / Inf do not count
+            if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
                 for (int k = 0; k < VPL; ++k)
                     if (!((finmask >> k) & 1u)) e[k] = 0.0f;
@@ -281,6 +284,7 @@ __global__ void __launch_bounds__(kThreads)
 compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, uint8_t* __restrict__ q,
                         uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned, bool out_aligned) {
     constexpr int VPL = G / 4;
+    constexpr uint32_t kAllFinite = VPL >= 32 ? 0xffffffffu : (1u << (VPL & 31)) - 1u;
     const int lane = threadIdx.x & 31;
     const int j = lane & 3;
     const uint32_t qmask = 0xFu << (lane & ~3);
@@ -332,7 +336,7 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             }
 #pragma unroll
             for (int i = 0; i < VPL; ++i) (void)quality_code(v[i], s, zp, r[i], e[i]);
-            if (finmask != (1u << VPL) - 1u) {  // rare: positions that held NaN / Inf do not count
+            if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
                 for (int i = 0; i < VPL; ++i)
                     if (!((finmask >> i) & 1u)) e[i] = 0.0f;
@@ -362,40 +366,117 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
     }
 }
 
+// ------------------------------------------------------------ symmetric codec
+
+__device__ __forceinline__ float clamp_i8(float v) { return fminf(fmaxf(v, -128.0f), 127.0f); }
+
+// src/tensorcache/codec.py:530-565 (tab.n == 0: scale = bf16(max|x| / 127)) and :568-620 (tab.n > 0: the
+// "adaptive" search over s0 * multiplier, scored on the raw values so that a NaN / Inf in the group
+// makes every score NaN / Inf and candidate 0 wins, then the winner rounded to bf16).  Signed codes.
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_sym_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                    uint16_t* __restrict__ scales, bool in_aligned, bool out_aligned) {
+    constexpr int VPL = G / 4;
+    constexpr uint32_t kAllFinite = VPL >= 32 ? 0xffffffffu : (1u << (VPL & 31)) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int j = lane & 3;
+    const uint32_t qmask = 0xFu << (lane & ~3);
+    const int64_t quads_per_grid = int64_t(gridDim.x) * (kThreads / 4);
+
+    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 4) + (threadIdx.x >> 2); g < ngroups; g += quads_per_grid) {
+        const int64_t base = g * G;
+        float v[VPL];
+        uint32_t finmask;
+        load_lane<G, T>(x, numel, base, j, in_aligned, v, finmask);
+
+        float lmax = fabsf(v[0]);
+#pragma unroll
+        for (int k = 1; k < VPL; ++k) lmax = fmaxf(lmax, fabsf(v[k]));
+        const float bmax = fmaxf(quad_max(lmax, qmask), 1e-8f);
+        const float s0 = __fdiv_rn(bmax, 127.0f);
+
+        float best_s = s0;
+        if (tab.n > 0) {
+            // a group that held a non-finite value scores NaN or +Inf under every candidate: candidate 0 wins
+            const bool all_finite = __all_sync(qmask, finmask == kAllFinite);
+            best_s = __fmul_rn(s0, tab.m[0]);
+            if (all_finite) {
+                float best_err = 0.0f;
+                for (int c = 0; c < tab.n; ++c) {
+                    const float s = __fmul_rn(s0, tab.m[c]);
+                    const float rcp = __frcp_rn(s);
+                    float e[VPL];
+#pragma unroll
+                    for (int k = 0; k < VPL; ++k) {
+                        const float qc = clamp_i8(quant_index(v[k], s, rcp, 0.0f));
+                        const float d = __fsub_rn(v[k], __fmul_rn(qc, s));
+                        e[k] = __fmul_rn(d, d);
+                    }
+                    const float err = quad_sum<G>(e, j, lane, qmask);
+                    if (c == 0 || err < best_err) {
+                        best_err = err;
+                        best_s = s;
+                    }
+                }
+            }
+        }
+        const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
+        const float sf = __uint_as_float(uint32_t(sbits) << 16);
+        uint8_t codes[VPL];
+#pragma unroll
+        for (int k = 0; k < VPL; ++k) {
+            const float qf = clamp_i8(rintf(__fdiv_rn(v[k], sf)));
+            codes[k] = ((finmask >> k) & 1u) ? uint8_t(int8_t(int(qf))) : uint8_t(0);
+        }
+        store_codes<G>(q, numel, base, j, out_aligned, codes);
+        if (j == 0) scales[g] = sbits;
+    }
+}
+
 // -------------------------------------------------------------------- dispatch
 
+enum class Coder { Legacy, Quality, Sym };
+
 template <int G, typename T>
-cudaError_t launch_typed(const void* x, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q, uint16_t* s,
-                         uint8_t* zp, int grid, cudaStream_t st) {
+cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q,
+                         uint16_t* s, uint8_t* zp, int grid, cudaStream_t st) {
     const T* xt = static_cast<const T*>(x);
     const bool in_aligned = (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0;
     const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
-    if (tab)
+    switch (coder) {
+    case Coder::Legacy:
         compress_legacy_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in_aligned, out_aligned);
-    else
+        break;
+    case Coder::Quality:
         compress_quality_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in_aligned, out_aligned);
+        break;
+    default:
+        compress_sym_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in_aligned, out_aligned);
+        break;
+    }
     return cudaGetLastError();
 }
 
 template <int G>
-cudaError_t launch_g(const void* x, int dtype, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q,
+cudaError_t launch_g(Coder coder, const void* x, int dtype, int64_t numel, int64_t ngroups, const CandTable* tab, uint8_t* q,
                      uint16_t* s, uint8_t* zp, int grid, cudaStream_t st) {
     switch (dtype) {
-    case TCB_DT_BF16: return launch_typed<G, __nv_bfloat16>(x, numel, ngroups, tab, q, s, zp, grid, st);
-    case TCB_DT_F16: return launch_typed<G, __half>(x, numel, ngroups, tab, q, s, zp, grid, st);
-    default: return launch_typed<G, float>(x, numel, ngroups, tab, q, s, zp, grid, st);
+    case TCB_DT_BF16: return launch_typed<G, __nv_bfloat16>(coder, x, numel, ngroups, tab, q, s, zp, grid, st);
+    case TCB_DT_F16: return launch_typed<G, __half>(coder, x, numel, ngroups, tab, q, s, zp, grid, st);
+    default: return launch_typed<G, float>(coder, x, numel, ngroups, tab, q, s, zp, grid, st);
     }
 }
 
-int compress_common(const char* who, const void* x, int dtype, int64_t numel, int group_size, const CandTable* tab,
-                    uint8_t* q, uint16_t* scales, uint8_t* zp, void* stream) {
+int compress_common(const char* who, Coder coder, const void* x, int dtype, int64_t numel, int group_size,
+                    const CandTable* tab, uint8_t* q, uint16_t* scales, uint8_t* zp, void* stream) {
     if (numel < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: numel %lld < 0", who, (long long)numel);
     if (!tcb::group_size_ok(group_size))
-        return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {8, 16, 24, 32, 48, 64, 128}", who, group_size);
     if (dtype != TCB_DT_BF16 && dtype != TCB_DT_F16 && dtype != TCB_DT_F32)
         return tcb::fail(TCB_ERR_BAD_ARG, "%s: dtype %d is not bf16(0) / f16(1) / f32(2)", who, dtype);
     if (numel == 0) return TCB_OK;
-    if (!x || !q || !scales || !zp) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);
+    if (!x || !q || !scales || (!zp && coder != Coder::Sym)) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);
     const size_t esz = dtype == TCB_DT_F32 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(x) % esz) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: x not aligned to its element size", who);
     if (reinterpret_cast<uintptr_t>(scales) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales not 2-byte aligned", who);
@@ -407,9 +488,13 @@ int compress_common(const char* who, const void* x, int dtype, int64_t numel, in
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (group_size) {
-    case 16: e = launch_g<16>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
-    case 32: e = launch_g<32>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
-    default: e = launch_g<64>(x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 8: e = launch_g<8>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 16: e = launch_g<16>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 24: e = launch_g<24>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 32: e = launch_g<32>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 48: e = launch_g<48>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    case 64: e = launch_g<64>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
+    default: e = launch_g<128>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;
     }
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
 }
@@ -424,10 +509,23 @@ extern "C" int tcb_compress_amo(const void* x, int dtype, int64_t numel, int gro
     CandTable tab;
     for (int i = 0; i < 64; ++i) tab.m[i] = i < n_cand ? multipliers[i] : 0.0f;
     tab.n = n_cand;
-    return compress_common("tcb_compress_amo", x, dtype, numel, group_size, &tab, q, scales, zp, stream);
+    return compress_common("tcb_compress_amo", Coder::Legacy, x, dtype, numel, group_size, &tab, q, scales, zp, stream);
 }
 
 extern "C" int tcb_compress_amo_quality(const void* x, int dtype, int64_t numel, int group_size, uint8_t* q,
                                         uint16_t* scales, uint8_t* zp, void* stream) {
-    return compress_common("tcb_compress_amo_quality", x, dtype, numel, group_size, nullptr, q, scales, zp, stream);
+    return compress_common("tcb_compress_amo_quality", Coder::Quality, x, dtype, numel, group_size, nullptr, q, scales, zp,
+                           stream);
+}
+
+extern "C" int tcb_compress_sym(const void* x, int dtype, int64_t numel, int group_size, const float* multipliers,
+                                int n_cand, int8_t* q, uint16_t* scales, void* stream) {
+    if (n_cand < 0 || n_cand > 64)
+        return tcb::fail(TCB_ERR_TOO_LARGE, "tcb_compress_sym: n_cand %d outside 0..64", n_cand);
+    if (n_cand > 0 && !multipliers) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_compress_sym: multipliers is null");
+    CandTable tab;
+    for (int i = 0; i < 64; ++i) tab.m[i] = i < n_cand ? multipliers[i] : 0.0f;
+    tab.n = n_cand;
+    return compress_common("tcb_compress_sym", Coder::Sym, x, dtype, numel, group_size, &tab,
+                           reinterpret_cast<uint8_t*>(q), scales, nullptr, stream);
 }

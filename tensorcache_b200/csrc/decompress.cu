@@ -21,6 +21,12 @@
 // a bf16 scale has at most 16 significant bits, so the fp32 product is exact and
 // the only rounding is the final round-to-nearest-even to bf16 -- the same value
 // the reference computes (src/tensorcache/codec.py:959-965).
+// The symmetric codec (signed codes, no zero point; src/tensorcache/codec.py:685-695)
+// runs through the same kernels with SYM = true: the sign bit of every code byte is
+// flipped, which turns the int8 value v into the unsigned byte v + 128, and the
+// zero point becomes the constant 128.
+// Group sizes: the 32- and 16-code kernels cover the powers of two 16..128; 8, 24
+// and 48 take a kernel that owns 8 codes per thread (no group straddles an octet).
 #include <cuda_bf16.h>
 
 #include "tcb_common.h"
@@ -60,10 +66,14 @@ __device__ __forceinline__ void convert_word(uint32_t w, float zmagic, float sca
     o1 = pack_bf16x2(__fmul_rn(__fsub_rn(f2, zmagic), scale), __fmul_rn(__fsub_rn(f3, zmagic), scale));
 }
 
+constexpr uint32_t kSignFlip = 0x80808080u;
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
 
-__device__ __forceinline__ uint16_t decode_one(uint8_t code, uint8_t z, uint16_t sbits) {
-    float v = __fmul_rn(__fsub_rn(float(code), float(z)), bf16_bits_to_float(sbits));
+template <bool SYM>
+__device__ __forceinline__ uint16_t decode_one(uint8_t code, const uint8_t* __restrict__ zp, int64_t g, uint16_t sbits) {
+    const float centred = SYM ? float(int8_t(code)) : __fsub_rn(float(code), float(zp[g]));
+    float v = __fmul_rn(centred, bf16_bits_to_float(sbits));
     __nv_bfloat16 b = __float2bfloat16_rn(v);
     return *reinterpret_cast<uint16_t*>(&b);
 }
@@ -82,12 +92,12 @@ __device__ __forceinline__ void stg_stream_v8(uint16_t* p, const uint32_t (&o)[8
 
 constexpr int kUnroll32 = 2;
 
-// Main kernel: 32 codes per thread.  LOG2_G = log2(group size) in {4, 5, 6}.
+// Main kernel: 32 codes per thread.  LOG2_G = log2(group size) in {4, 5, 6, 7}.
 // Needs q and out 32-byte aligned.  Every block owns one contiguous, equally
 // sized range of 32-code units; the grid is exactly the number of blocks the
 // device holds at once, so there is a single wave and no block does more work
 // than another.
-template <int LOG2_G>
+template <int LOG2_G, bool SYM>
 __global__ void __launch_bounds__(kThreads)
 decompress_v8_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales,
                      const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel) {
@@ -113,12 +123,19 @@ decompress_v8_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__
                 if (LOG2_G == 4) {  // two groups of 16 per unit
                     sb[u][0] = __ldg(scales + 2 * t);
                     sb[u][1] = __ldg(scales + 2 * t + 1);
-                    zb[u][0] = __ldg(zp + 2 * t);
-                    zb[u][1] = __ldg(zp + 2 * t + 1);
-                } else {  // one group (G32) or half a group (G64)
-                    const int64_t g = t >> (LOG2_G - 5);
+                    if (!SYM) {
+                        zb[u][0] = __ldg(zp + 2 * t);
+                        zb[u][1] = __ldg(zp + 2 * t + 1);
+                    }
+                } else {  // one group (G32) or part of a group (G64, G128)
+                    const int64_t g = t >> (LOG2_G >= 5 ? LOG2_G - 5 : 0);
                     sb[u][0] = sb[u][1] = __ldg(scales + g);
-                    zb[u][0] = zb[u][1] = __ldg(zp + g);
+                    if (!SYM) zb[u][0] = zb[u][1] = __ldg(zp + g);
+                }
+                if (SYM) {
+                    zb[u][0] = zb[u][1] = 128;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) w[u][k] ^= kSignFlip;
                 }
             }
         }
@@ -146,13 +163,13 @@ decompress_v8_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__
     if (blockIdx.x == 0 && threadIdx.x < tail) {
         const int64_t i = (units << 5) + threadIdx.x;
         const int64_t g = i >> LOG2_G;
-        out[i] = decode_one(q[i], zp[g], scales[g]);
+        out[i] = decode_one<SYM>(q[i], zp, g, scales[g]);
     }
 }
 
 // Variant for pointers that are 16- but not 32-byte aligned: 16 codes per thread,
 // 128-bit load, two 128-bit stores.  LOG2_CPG = log2(G / 16).
-template <int LOG2_CPG>
+template <int LOG2_CPG, bool SYM>
 __global__ void __launch_bounds__(kThreads)
 decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ scales,
                       const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel) {
@@ -177,7 +194,12 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
                 w[u] = ldg_stream_v4(q + c);
                 const int64_t g = c >> LOG2_CPG;
                 sb[u] = __ldg(scales + g);
-                zb[u] = __ldg(zp + g);
+                if (SYM) {
+                    zb[u] = 128;
+                    w[u].x ^= kSignFlip, w[u].y ^= kSignFlip, w[u].z ^= kSignFlip, w[u].w ^= kSignFlip;
+                } else {
+                    zb[u] = __ldg(zp + g);
+                }
             }
         }
 #pragma unroll
@@ -201,17 +223,73 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
     if (blockIdx.x == 0 && threadIdx.x < tail) {
         const int64_t i = (full_chunks << 4) + threadIdx.x;
         const int64_t g = i >> (LOG2_CPG + 4);
-        out[i] = decode_one(reinterpret_cast<const uint8_t*>(q)[i], zp[g], scales[g]);
+        out[i] = decode_one<SYM>(reinterpret_cast<const uint8_t*>(q)[i], zp, g, scales[g]);
+    }
+}
+
+// Group sizes that are a multiple of 8 but not a power of two >= 16 (8, 24, 48): 8 codes per
+// thread, one 64-bit load and one 128-bit store; OPG = octets per group.  Needs q 8-byte and out
+// 16-byte aligned.
+template <int OPG, bool SYM>
+__global__ void __launch_bounds__(kThreads)
+decompress_oct_kernel(const uint2* __restrict__ q, const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zp,
+                      uint16_t* __restrict__ out, int64_t numel) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int64_t octs = numel >> 3;
+    const int64_t begin = octs * blockIdx.x / gridDim.x;
+    const int64_t end = octs * (blockIdx.x + 1) / gridDim.x;
+
+    for (int64_t c0 = begin + threadIdx.x; c0 < end; c0 += int64_t(kThreads) * kUnroll) {
+        uint2 w[kUnroll];
+        uint16_t sb[kUnroll];
+        uint8_t zb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t c = c0 + int64_t(u) * kThreads;
+            if (c < end) {
+                w[u] = __ldg(q + c);
+                const int64_t g = c / OPG;
+                sb[u] = __ldg(scales + g);
+                if (SYM) {
+                    zb[u] = 128;
+                    w[u].x ^= kSignFlip, w[u].y ^= kSignFlip;
+                } else {
+                    zb[u] = __ldg(zp + g);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t c = c0 + int64_t(u) * kThreads;
+            if (c < end) {
+                const float scale = bf16_bits_to_float(sb[u]);
+                const float zmagic = 8388608.0f + float(zb[u]);
+                uint32_t o0, o1, o2, o3;
+                convert_word(w[u].x, zmagic, scale, o0, o1);
+                convert_word(w[u].y, zmagic, scale, o2, o3);
+                *reinterpret_cast<uint4*>(out + (c << 3)) = make_uint4(o0, o1, o2, o3);
+            }
+        }
+    }
+
+    const int tail = int(numel & 7);
+    if (blockIdx.x == 0 && threadIdx.x < tail) {
+        const int64_t i = (octs << 3) + threadIdx.x;
+        const int64_t g = i / (8 * OPG);
+        out[i] = decode_one<SYM>(reinterpret_cast<const uint8_t*>(q)[i], zp, g, scales[g]);
     }
 }
 
 // Any alignment, one value per thread-iteration.  Same arithmetic as above.
+template <bool SYM>
 __global__ void __launch_bounds__(kThreads)
 decompress_scalar_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales,
-                         const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel, int log2_g) {
+                         const uint8_t* __restrict__ zp, uint16_t* __restrict__ out, int64_t numel, int group_size) {
     for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < numel; i += int64_t(gridDim.x) * kThreads) {
-        const int64_t g = i >> log2_g;
-        out[i] = decode_one(q[i], zp[g], scales[g]);
+        const int64_t g = i / group_size;
+        out[i] = decode_one<SYM>(q[i], zp, g, scales[g]);
     }
 }
 
@@ -248,41 +326,59 @@ cudaError_t launch_one_wave(K kernel, int* cache, int64_t units, QPtr q, const u
     return cudaLaunchKernelEx(&cfg, kernel, q, s, zp, out, numel);
 }
 
-template <int LOG2_G>
+template <int LOG2_G, bool SYM>
 cudaError_t launch_aligned(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel,
                            bool aligned32, cudaStream_t st) {
     static int cache32[64] = {0}, cache16[64] = {0};
-    if (aligned32) return launch_one_wave(decompress_v8_kernel<LOG2_G>, cache32, numel >> 5, q, s, zp, out, numel, st);
-    return launch_one_wave(decompress_vec_kernel<LOG2_G - 4>, cache16, numel >> 4, reinterpret_cast<const uint4*>(q), s, zp, out,
+    if (aligned32) return launch_one_wave(decompress_v8_kernel<LOG2_G, SYM>, cache32, numel >> 5, q, s, zp, out, numel, st);
+    return launch_one_wave(decompress_vec_kernel<LOG2_G - 4, SYM>, cache16, numel >> 4, reinterpret_cast<const uint4*>(q), s,
+                           zp, out, numel, st);
+}
+
+template <int OPG, bool SYM>
+cudaError_t launch_oct(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel, cudaStream_t st) {
+    static int cache[64] = {0};
+    return launch_one_wave(decompress_oct_kernel<OPG, SYM>, cache, numel >> 3, reinterpret_cast<const uint2*>(q), s, zp, out,
                            numel, st);
+}
+
+template <bool SYM>
+int launch_any(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel, int group_size,
+               cudaStream_t st) {
+    const uintptr_t qa = reinterpret_cast<uintptr_t>(q), oa = reinterpret_cast<uintptr_t>(out);
+    const bool pow2_wide = group_size == 16 || group_size == 32 || group_size == 64 || group_size == 128;
+    const bool vector_ok = pow2_wide ? ((qa | oa) & 15) == 0 : ((qa & 7) == 0 && (oa & 15) == 0);
+    if (!vector_ok) {
+        int64_t blocks = (numel + kThreads - 1) / kThreads;
+        const int64_t cap = int64_t(tcb::sm_count()) * 16;
+        decompress_scalar_kernel<SYM><<<int(blocks < cap ? blocks : cap), kThreads, 0, st>>>(q, scales, zp, out, numel, group_size);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, "decompress_scalar_kernel launch");
+    }
+    const bool aligned32 = ((qa | oa) & 31) == 0;
+    cudaError_t e;
+    switch (group_size) {
+    case 8: e = launch_oct<1, SYM>(q, scales, zp, out, numel, st); break;
+    case 24: e = launch_oct<3, SYM>(q, scales, zp, out, numel, st); break;
+    case 48: e = launch_oct<6, SYM>(q, scales, zp, out, numel, st); break;
+    case 16: e = launch_aligned<4, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    case 32: e = launch_aligned<5, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    case 64: e = launch_aligned<6, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    default: e = launch_aligned<7, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    }
+    return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, "decompress kernel launch");
 }
 
 }  // namespace
 
 namespace tcb {
 
-// Shared by the public entry point and the streamer.
+// Shared by the public entry points and the streamer.  zp == nullptr selects the symmetric codec.
 int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,
                       int group_size, cudaStream_t st) {
     if (numel == 0) return TCB_OK;
-    const int sms = sm_count();
-    const bool aligned16 = (reinterpret_cast<uintptr_t>(q) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-    if (!aligned16) {
-        const int log2g = group_size == 16 ? 4 : group_size == 32 ? 5 : 6;
-        int64_t blocks = (numel + kThreads - 1) / kThreads;
-        int grid = int(blocks < int64_t(sms) * 16 ? blocks : int64_t(sms) * 16);
-        decompress_scalar_kernel<<<grid, kThreads, 0, st>>>(q, scales, zp, out, numel, log2g);
-        cudaError_t e = cudaGetLastError();
-        return e == cudaSuccess ? TCB_OK : cuda_fail(e, "decompress_scalar_kernel launch");
-    }
-    const bool aligned32 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out)) & 31) == 0;
-    cudaError_t e;
-    switch (group_size) {
-    case 16: e = launch_aligned<4>(q, scales, zp, out, numel, aligned32, st); break;
-    case 32: e = launch_aligned<5>(q, scales, zp, out, numel, aligned32, st); break;
-    default: e = launch_aligned<6>(q, scales, zp, out, numel, aligned32, st); break;
-    }
-    return e == cudaSuccess ? TCB_OK : cuda_fail(e, "decompress kernel launch");
+    return zp ? launch_any<false>(q, scales, zp, out, numel, group_size, st)
+              : launch_any<true>(q, scales, nullptr, out, numel, group_size, st);
 }
 
 }  // namespace tcb
@@ -291,10 +387,23 @@ extern "C" int tcb_decompress_amo(const uint8_t* q, const uint16_t* scales, cons
                                   int64_t numel, int group_size, void* stream) {
     if (numel < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_decompress_amo: numel %lld < 0", (long long)numel);
     if (!tcb::group_size_ok(group_size))
-        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_decompress_amo: group_size %d not in {16, 32, 64}", group_size);
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_decompress_amo: group_size %d not in {8, 16, 24, 32, 48, 64, 128}", group_size);
     if (numel == 0) return TCB_OK;
     if (!q || !scales || !zp || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_decompress_amo: null pointer");
     if (reinterpret_cast<uintptr_t>(scales) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "tcb_decompress_amo: scales not 2-byte aligned");
     if (reinterpret_cast<uintptr_t>(out) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "tcb_decompress_amo: out not 2-byte aligned");
     return tcb::launch_decompress(q, scales, zp, out, numel, group_size, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tcb_decompress_sym(const int8_t* q, const uint16_t* scales, uint16_t* out, int64_t numel, int group_size,
+                                  void* stream) {
+    if (numel < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_decompress_sym: numel %lld < 0", (long long)numel);
+    if (!tcb::group_size_ok(group_size))
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_decompress_sym: group_size %d not in {8, 16, 24, 32, 48, 64, 128}", group_size);
+    if (numel == 0) return TCB_OK;
+    if (!q || !scales || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_decompress_sym: null pointer");
+    if (reinterpret_cast<uintptr_t>(scales) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "tcb_decompress_sym: scales not 2-byte aligned");
+    if (reinterpret_cast<uintptr_t>(out) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "tcb_decompress_sym: out not 2-byte aligned");
+    return tcb::launch_decompress(reinterpret_cast<const uint8_t*>(q), scales, nullptr, out, numel, group_size,
+                                  static_cast<cudaStream_t>(stream));
 }

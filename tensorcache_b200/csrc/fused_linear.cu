@@ -572,7 +572,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
                                         int group_size, int quant_is_rhs, void* stream) {
     const char* who = "tcb_fused_dequant_linear";
     if (R_d < 0 || R_q < 0 || K < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: negative size", who);
-    if (!tcb::group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+    if (!tcb::core_group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
     if (R_d == 0 || R_q == 0) return TCB_OK;
     if (K == 0 || K % kBlockK != 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: K = %lld must be a positive multiple of %d", who, (long long)K, kBlockK);
     if (!dense || !q || !scales || !out) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);

@@ -52,7 +52,7 @@ extern "C" int tcb_decompress_amo_host_noalloc(const uint8_t* q_host, const uint
                                                uint16_t* out_dev, int64_t numel, int group_size, void* stream) {
     const char* who = "tcb_decompress_amo_host_noalloc";
     if (numel < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: numel %lld < 0", who, (long long)numel);
-    if (!tcb::group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+    if (!tcb::core_group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
     if (numel > kMaxValues)
         return tcb::fail(TCB_ERR_TOO_LARGE, "%s: %lld values asked, the built-in staging area holds at most %lld per call "
                          "(split the tensor at a multiple of the group size)", who, (long long)numel, (long long)kMaxValues);

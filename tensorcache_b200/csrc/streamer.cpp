@@ -234,6 +234,7 @@ struct tcb_streamer {
     const uint4** row_tables_dev = nullptr;   // the same memory as the device addresses it
     std::vector<const uint8_t*> q_dev, s_dev, zp_dev;  // device views of the page-locked mappings
     bool rows_vectorisable = false;
+    bool has_zp = true;  // false: symmetric cache (signed codes, no zero-point file)
 
     std::thread producer;
     std::mutex mu;
@@ -320,7 +321,7 @@ void producer_main(tcb_streamer* s) {
             if (!s->d.direct_dma) {
                 gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_q[slot]), qrow, rows, src(s->q_bases, qrow));
                 gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
-                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+                if (s->has_zp) gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
             }
             // the consumer's last read of this device slot (this pass or the one before)
             e = cudaStreamWaitEvent(s->copy_stream, s->released[slot], 0);
@@ -329,7 +330,7 @@ void producer_main(tcb_streamer* s) {
                 e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
                 if (e == cudaSuccess)
                     e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
-                if (e == cudaSuccess)
+                if (e == cudaSuccess && s->has_zp)
                     e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
             } else {
                 // The mapped shards are page-locked: the copy engine reads them directly.  Runs of
@@ -365,17 +366,18 @@ void producer_main(tcb_streamer* s) {
                         locate(s, idx ? idx[i] : first + i, sh, local);
                         tq[i] = reinterpret_cast<const uint4*>(s->q_dev[sh] + local * qrow);
                         ts[i] = reinterpret_cast<const uint4*>(s->s_dev[sh] + local * srow);
-                        tz[i] = reinterpret_cast<const uint4*>(s->zp_dev[sh] + local * zrow);
+                        if (s->has_zp) tz[i] = reinterpret_cast<const uint4*>(s->zp_dev[sh] + local * zrow);
                     }
                     const uint4** dq = s->row_tables_dev + o;
                     gather_host_rows_kernel<<<48, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_q[slot]), dq, qrow / 16, rows);
                     gather_host_rows_kernel<<<8, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_s[slot]), dq + B, srow / 16, rows);
-                    gather_host_rows_kernel<<<8, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_zp[slot]), dq + 2 * B, zrow / 16, rows);
+                    if (s->has_zp)
+                        gather_host_rows_kernel<<<8, 256, 0, s->copy_stream>>>(static_cast<uint4*>(s->dev_zp[slot]), dq + 2 * B, zrow / 16, rows);
                     e = cudaGetLastError();
                 } else {
                     if (scattered) {
                         gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
-                        gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+                        if (s->has_zp) gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
                     }
                     for (size_t r = 0; e == cudaSuccess && r < run_first.size(); ++r) {
                         const int sh = run_shard[r];
@@ -385,13 +387,13 @@ void producer_main(tcb_streamer* s) {
                         if (!scattered && e == cudaSuccess)
                             e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_s[slot]) + at * srow, s->s_bases[sh] + loc * srow, size_t(n * srow),
                                                 cudaMemcpyHostToDevice, s->copy_stream);
-                        if (!scattered && e == cudaSuccess)
+                        if (!scattered && e == cudaSuccess && s->has_zp)
                             e = cudaMemcpyAsync(static_cast<uint8_t*>(s->dev_zp[slot]) + at * zrow, s->zp_bases[sh] + loc * zrow, size_t(n * zrow),
                                                 cudaMemcpyHostToDevice, s->copy_stream);
                     }
                     if (scattered && e == cudaSuccess)
                         e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
-                    if (scattered && e == cudaSuccess)
+                    if (scattered && e == cudaSuccess && s->has_zp)
                         e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
                 }
             }
@@ -452,7 +454,7 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
     if (!desc || !out) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null argument");
     *out = nullptr;
     if (!tcb::group_size_ok(desc->group_size))
-        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_streamer_create: group_size %d not in {16, 32, 64}", desc->group_size);
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "tcb_streamer_create: group_size %d not in {8, 16, 24, 32, 48, 64, 128}", desc->group_size);
     if (desc->n_slots < 1 || desc->n_slots > 8) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: n_slots %d outside 1..8", desc->n_slots);
     if (desc->n_shards < 1 || desc->n_shards > 4096) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: n_shards %d outside 1..4096", desc->n_shards);
     if (desc->batch_size < 1 || desc->values_per_sample < 1) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: bad sizes");
@@ -462,27 +464,30 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
         return tcb::fail(TCB_ERR_BAD_ARG,
                          "tcb_streamer_create: values per sample (%lld) must be a multiple of the group size so that "
                          "a batch decodes as one flat tensor", (long long)desc->values_per_sample);
-    if (!desc->q_bases || !desc->s_bases || !desc->zp_bases || !desc->shard_sizes)
+    if (!desc->q_bases || !desc->s_bases || !desc->shard_sizes)
         return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null shard table");
+    const bool has_zp = desc->zp_bases != nullptr;  // a symmetric cache has no zero points
     for (int i = 0; i < desc->n_shards; ++i) {
         if (desc->shard_sizes[i] < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: shard %d has negative size", i);
-        if (desc->shard_sizes[i] > 0 && (!desc->q_bases[i] || !desc->s_bases[i] || !desc->zp_bases[i]))
+        if (desc->shard_sizes[i] > 0 && (!desc->q_bases[i] || !desc->s_bases[i] || (has_zp && !desc->zp_bases[i])))
             return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: shard %d has a null mapping", i);
     }
-    if (!desc->pinned_q || !desc->pinned_s || !desc->pinned_zp || !desc->dev_q || !desc->dev_s || !desc->dev_zp || !desc->dev_out)
+    if (!desc->pinned_q || !desc->pinned_s || !desc->dev_q || !desc->dev_s || !desc->dev_out ||
+        (has_zp && (!desc->pinned_zp || !desc->dev_zp)))
         return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer table");
     for (int i = 0; i < desc->n_slots; ++i)
-        if ((!desc->pinned_q[i] && !desc->direct_dma) || !desc->pinned_s[i] || !desc->pinned_zp[i] || !desc->dev_q[i] || !desc->dev_s[i] ||
-            !desc->dev_zp[i] || !desc->dev_out[i])
+        if ((!desc->pinned_q[i] && !desc->direct_dma) || !desc->pinned_s[i] || !desc->dev_q[i] || !desc->dev_s[i] || !desc->dev_out[i] ||
+            (has_zp && (!desc->pinned_zp[i] || !desc->dev_zp[i])))
             return tcb::fail(TCB_ERR_BAD_ARG, "tcb_streamer_create: null buffer in slot %d", i);
 
     tcb_streamer* s = new tcb_streamer();
     s->d = *desc;
+    s->has_zp = has_zp;
     int64_t total = 0;
     for (int i = 0; i < desc->n_shards; ++i) {
         s->q_bases.push_back(static_cast<const uint8_t*>(desc->q_bases[i]));
         s->s_bases.push_back(static_cast<const uint8_t*>(desc->s_bases[i]));
-        s->zp_bases.push_back(static_cast<const uint8_t*>(desc->zp_bases[i]));
+        s->zp_bases.push_back(has_zp ? static_cast<const uint8_t*>(desc->zp_bases[i]) : nullptr);
         s->shard_start.push_back(total);
         total += desc->shard_sizes[i];
     }
@@ -490,10 +495,10 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
     for (int i = 0; i < desc->n_slots; ++i) {
         s->pinned_q.push_back(desc->pinned_q[i]);
         s->pinned_s.push_back(desc->pinned_s[i]);
-        s->pinned_zp.push_back(desc->pinned_zp[i]);
+        s->pinned_zp.push_back(has_zp ? desc->pinned_zp[i] : nullptr);
         s->dev_q.push_back(desc->dev_q[i]);
         s->dev_s.push_back(desc->dev_s[i]);
-        s->dev_zp.push_back(desc->dev_zp[i]);
+        s->dev_zp.push_back(has_zp ? desc->dev_zp[i] : nullptr);
         s->dev_out.push_back(desc->dev_out[i]);
     }
     // the caller's tables need not outlive this call
@@ -519,7 +524,8 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
     }
     if (desc->direct_dma) {
         // the gather kernel moves 16-byte units: rows and mapping bases must be multiples of 16 bytes
-        bool ok16 = desc->values_per_sample % 16 == 0 && (desc->groups_per_sample * 2) % 16 == 0 && desc->groups_per_sample % 16 == 0;
+        bool ok16 = desc->values_per_sample % 16 == 0 && (desc->groups_per_sample * 2) % 16 == 0 &&
+                    (!has_zp || desc->groups_per_sample % 16 == 0);
         for (int i = 0; i < desc->n_shards; ++i)
             ok16 = ok16 && ((reinterpret_cast<uintptr_t>(s->q_bases[i]) | reinterpret_cast<uintptr_t>(s->s_bases[i]) |
                              reinterpret_cast<uintptr_t>(s->zp_bases[i])) & 15) == 0;
@@ -532,7 +538,7 @@ extern "C" int tcb_streamer_create(const tcb_streamer_desc* desc, tcb_streamer**
             if (desc->shard_sizes[i] > 0 &&
                 (cudaHostGetDevicePointer(&dq, const_cast<uint8_t*>(s->q_bases[i]), 0) != cudaSuccess ||
                  cudaHostGetDevicePointer(&ds, const_cast<uint8_t*>(s->s_bases[i]), 0) != cudaSuccess ||
-                 cudaHostGetDevicePointer(&dz, const_cast<uint8_t*>(s->zp_bases[i]), 0) != cudaSuccess)) {
+                 (has_zp && cudaHostGetDevicePointer(&dz, const_cast<uint8_t*>(s->zp_bases[i]), 0) != cudaSuccess))) {
                 cudaGetLastError();
                 ok16 = false;
             }
@@ -644,7 +650,8 @@ extern "C" int tcb_streamer_next(tcb_streamer* s, void* consumer_stream, int* sl
     if (rc != TCB_OK || *rows_out == 0) return rc;
     const int slot = *slot_out;
     rc = tcb::launch_decompress(static_cast<const uint8_t*>(s->dev_q[slot]), static_cast<const uint16_t*>(s->dev_s[slot]),
-                                static_cast<const uint8_t*>(s->dev_zp[slot]), static_cast<uint16_t*>(s->dev_out[slot]),
+                                s->has_zp ? static_cast<const uint8_t*>(s->dev_zp[slot]) : nullptr,
+                                static_cast<uint16_t*>(s->dev_out[slot]),
                                 int64_t(*rows_out) * s->d.values_per_sample, s->d.group_size,
                                 static_cast<cudaStream_t>(consumer_stream));
     int rc2 = tcb_streamer_release(s, consumer_stream);

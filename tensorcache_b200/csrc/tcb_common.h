@@ -24,7 +24,9 @@ inline int cuda_fail(cudaError_t e, const char* what) {
         if (_e != cudaSuccess) return ::tcb::cuda_fail(_e, #expr); \
     } while (0)
 
-inline bool group_size_ok(int g) { return g == 16 || g == 32 || g == 64; }
+// Group sizes of the codec kernels (encode and decode); the fused GEMM and the no-allocation decode accept 16 / 32 / 64 only.
+inline bool group_size_ok(int g) { return g == 8 || g == 16 || g == 24 || g == 32 || g == 48 || g == 64 || g == 128; }
+inline bool core_group_size_ok(int g) { return g == 16 || g == 32 || g == 64; }
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

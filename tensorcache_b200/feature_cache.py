@@ -6,7 +6,8 @@ little-endian arrays ``<prefix>[_shard{i}]_int8.bin`` (uint8 ``[N, seq, dim]``),
 ``_scales.bin`` (uint16 = bf16 bits ``[N, groups]``), ``_zp.bin`` (uint8
 ``[N, groups]``), a ``_meta.json`` per file set and a ``<prefix>_shards.json``
 manifest for sharded caches.  Caches written here are readable by the reference
-and vice versa.  Only AMO-BQ caches (``amo_bq=True``) are supported.
+and vice versa.  Caches of the symmetric codec (``amo_bq=False``, optionally
+``adaptive=True``) hold int8 codes and have no ``_zp.bin``.
 """
 from __future__ import annotations
 
@@ -22,7 +23,7 @@ import ctypes
 
 from . import _lib
 from ._pipeline import NativePipeline, default_gather_threads, open_cache
-from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq
+from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, dequantize_int8_g32
 
 
 class FeatureCacheWriter:
@@ -53,8 +54,6 @@ class FeatureCacheWriter:
             raise ValueError(f"Feature caches with {quant_bits}-bit are not supported")
         if quant_bits != 8:
             raise ValueError(f"quant_bits must be 8 for features, got {quant_bits}")
-        if not amo_bq:
-            raise NotImplementedError("only AMO-BQ caches (amo_bq=True) are written on the B200 path")
         if amo_mode is not None:
             if amo_mode not in AMO_BQ_PRESETS:
                 raise ValueError(f"Unknown amo_mode {amo_mode!r}, choose from {list(AMO_BQ_PRESETS.keys())}")
@@ -63,8 +62,8 @@ class FeatureCacheWriter:
         self.group_size, self.adaptive, self.amo_bq = group_size, adaptive, amo_bq
         self.amo_mode, self.amo_lo, self.amo_hi, self.amo_candidates = amo_mode, amo_lo, amo_hi, amo_candidates
         self.quant_bits = quant_bits
-        self.codec = BlockwiseInt8Codec(group_size=group_size, amo_bq=True, amo_lo=amo_lo, amo_hi=amo_hi,
-                                        amo_candidates=amo_candidates, amo_mode=amo_mode)
+        self.codec = BlockwiseInt8Codec(group_size=group_size, adaptive=adaptive, amo_bq=amo_bq, amo_lo=amo_lo, amo_hi=amo_hi,
+                                        amo_candidates=amo_candidates, amo_mode=amo_mode if amo_bq else None)
         self.num_shards = max(1, int(num_shards))
         self.elements_per_sample = seq_len * dim
         self.scales_per_sample = (self.elements_per_sample + group_size - 1) // group_size
@@ -94,15 +93,16 @@ class FeatureCacheWriter:
             if resume:
                 self._grow_file(paths[0], sz * seq_len * dim)
                 self._grow_file(paths[1], sz * self.scales_per_sample * 2)
-                self._grow_file(paths[2], sz * self.scales_per_sample)
-            self._maps.append((
-                np.memmap(paths[0], dtype=np.uint8, mode=mode, shape=(sz, seq_len, dim)),
-                np.memmap(paths[1], dtype=np.uint16, mode=mode, shape=(sz, self.scales_per_sample)),
-                np.memmap(paths[2], dtype=np.uint8, mode=mode, shape=(sz, self.scales_per_sample)),
-            ))
+                if amo_bq:
+                    self._grow_file(paths[2], sz * self.scales_per_sample)
+            maps = [np.memmap(paths[0], dtype=np.uint8 if amo_bq else np.int8, mode=mode, shape=(sz, seq_len, dim)),
+                    np.memmap(paths[1], dtype=np.uint16, mode=mode, shape=(sz, self.scales_per_sample))]
+            if amo_bq:
+                maps.append(np.memmap(paths[2], dtype=np.uint8, mode=mode, shape=(sz, self.scales_per_sample)))
+            self._maps.append(tuple(maps))
         self.int8_path = self.shard_prefixes[0] + "_int8.bin"
         self.scales_path = self.shard_prefixes[0] + "_scales.bin"
-        self.zp_path = self.shard_prefixes[0] + "_zp.bin"
+        self.zp_path = self.shard_prefixes[0] + "_zp.bin" if amo_bq else None
         self.current_idx = 0
         self._closed = False
         self._staging = None
@@ -174,9 +174,9 @@ class FeatureCacheWriter:
             pin = torch.cuda.is_available()
             n = self._CHUNK
             self._staging = [(
-                torch.empty((n, self.seq_len, self.dim), dtype=torch.uint8, pin_memory=pin),
+                torch.empty((n, self.seq_len, self.dim), dtype=torch.uint8 if self.amo_bq else torch.int8, pin_memory=pin),
                 torch.empty((n, self.scales_per_sample), dtype=torch.int16, pin_memory=pin),
-                torch.empty((n, self.scales_per_sample), dtype=torch.uint8, pin_memory=pin),
+                torch.empty((n, self.scales_per_sample), dtype=torch.uint8, pin_memory=pin) if self.amo_bq else None,
             ) for _ in range(2)]
         return self._staging[which]
 
@@ -213,11 +213,13 @@ class FeatureCacheWriter:
             sub = tensor_bf16[done:done + cur]
             if not sub.is_cuda:
                 sub = sub.cuda(non_blocking=True)
-            q, s, zp, _ = self.codec.quantize(sub)
+            enc = self.codec.quantize(sub)      # (q, s, zp, shape) for AMO-BQ, (q, s, shape) for the symmetric codec
+            q, s = enc[0], enc[1]
             hq, hs, hz = self._host_staging(k & 1)
             hq[:cur].copy_(q.view(cur, self.seq_len, self.dim), non_blocking=True)
             hs[:cur].copy_(s.view(torch.int16).view(cur, self.scales_per_sample), non_blocking=True)
-            hz[:cur].copy_(zp.view(cur, self.scales_per_sample), non_blocking=True)
+            if self.amo_bq:
+                hz[:cur].copy_(enc[2].view(cur, self.scales_per_sample), non_blocking=True)
             event = torch.cuda.Event()
             event.record(torch.cuda.current_stream(q.device))
             if pending is not None:
@@ -232,13 +234,14 @@ class FeatureCacheWriter:
     def _meta(self, num_samples: int, prefix: str, with_bits: bool) -> dict:
         meta = {
             "num_samples": num_samples, "seq_len": self.seq_len, "dim": self.dim, "group_size": self.group_size,
-            "adaptive": self.adaptive, "amo_bq": self.amo_bq, "amo_mode": self.amo_mode, "amo_lo": self.amo_lo,
-            "amo_hi": self.amo_hi, "amo_candidates": self.amo_candidates,
+            "adaptive": self.adaptive, "amo_bq": self.amo_bq, "amo_mode": self.amo_mode if self.amo_bq else None,
+            "amo_lo": self.amo_lo if self.amo_bq else None, "amo_hi": self.amo_hi if self.amo_bq else None,
+            "amo_candidates": self.amo_candidates if self.amo_bq else None,
         }
         if with_bits:
             meta["quant_bits"] = self.quant_bits
         meta.update(int8_file=os.path.basename(prefix + "_int8.bin"), scales_file=os.path.basename(prefix + "_scales.bin"),
-                    zp_file=os.path.basename(prefix + "_zp.bin"))
+                    zp_file=os.path.basename(prefix + "_zp.bin") if self.amo_bq else None)
         return meta
 
     def close(self):
@@ -274,9 +277,9 @@ class FeatureCacheWriter:
 
 
 class FeatureCacheDataset(torch.utils.data.Dataset):
-    """Memory-mapped reader: ``ds[i]`` returns copies ``(q, scales, zp)`` (or the
-    decoded bf16 sample on ``auto_dequant_device``); ``iter_batches`` streams
-    decoded batches through the native pipeline.
+    """Memory-mapped reader: ``ds[i]`` returns copies ``(q, scales, zp)`` -- ``(q, scales)`` for a
+    cache of the symmetric codec -- or the decoded bf16 sample on ``auto_dequant_device``;
+    ``iter_batches`` streams decoded batches through the native pipeline.
 
     ``rank`` / ``world_size`` select shard ``rank % num_shards`` like
     ``ZeroCopyTensorStreamer`` does.  (The reference class computes that mapping
@@ -310,6 +313,12 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
         sh = self._layout.shards[si]
         q = torch.from_numpy(np.array(sh.q[li]))
         s = torch.from_numpy(np.array(sh.s[li]).view(np.int16)).view(torch.bfloat16)
+        if not self.amo_bq:
+            if self.auto_dequant_device is not None:
+                dev = self.auto_dequant_device
+                return dequantize_int8_g32(q.to(dev, non_blocking=True), s.to(dev, non_blocking=True),
+                                           (self.seq_len, self.dim), group_size=self.group_size)
+            return q, s
         zp = torch.from_numpy(np.array(sh.zp[li]))
         if self.auto_dequant_device is not None:
             dev = self.auto_dequant_device
@@ -320,7 +329,8 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
     def iter_batches(self, batch_size: int = 128, shuffle: bool = True, device: str = "cuda:0", dequantize: bool = True):
         """Yields bf16 ``[rows, seq_len, dim]`` views of a two-slot output ring
         (valid until two more batches have been requested), or cloned
-        ``(q, scales, zp)`` device tensors when ``dequantize=False``."""
+        ``(q, scales, zp)`` device tensors (``(q, scales)`` for a symmetric cache) when
+        ``dequantize=False``."""
         pipe = NativePipeline(self._layout, batch_size, torch.device(device), n_slots=2)
         self._pipes.append(pipe)
         try:
@@ -340,7 +350,9 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
                     slot, rows = pipe.acquire()
                     if rows == 0:
                         break
-                    out = (pipe.dev_q[slot][:rows].clone(), pipe.dev_s[slot][:rows].clone(), pipe.dev_zp[slot][:rows].clone())
+                    out = (pipe.dev_q[slot][:rows].clone(), pipe.dev_s[slot][:rows].clone())
+                    if self.amo_bq:
+                        out += (pipe.dev_zp[slot][:rows].clone(),)
                     pipe.release()
                     yield out
         finally:

@@ -22,7 +22,8 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .codec import SUPPORTED_GROUP_SIZES
+
+SUPPORTED_GROUP_SIZES = (16, 32, 64)  # group sizes the tensor-core kernel is instantiated for
 
 
 def _ptr(t: Optional[torch.Tensor]):

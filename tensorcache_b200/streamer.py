@@ -113,8 +113,9 @@ class ZeroCopyTensorStreamer:
             self.out_bf16 = self._pipe.dev_out
             self.out_bf16_0 = self.out_bf16[0]
             self.out_bf16_1 = self.out_bf16[1] if len(self.out_bf16) > 1 else self.out_bf16[0]
-            self.gpu_int8, self.gpu_scales, self.gpu_zp = self._pipe.dev_q, self._pipe.dev_s, self._pipe.dev_zp
-            self.pinned_int8, self.pinned_scales, self.pinned_zp = self._pipe.pinned_q, self._pipe.pinned_s, self._pipe.pinned_zp
+            none = [None] * self.n_bufs   # a cache of the symmetric codec has no zero points
+            self.gpu_int8, self.gpu_scales, self.gpu_zp = self._pipe.dev_q, self._pipe.dev_s, self._pipe.dev_zp or none
+            self.pinned_int8, self.pinned_scales, self.pinned_zp = self._pipe.pinned_q, self._pipe.pinned_s, self._pipe.pinned_zp or none
         return self._pipe
 
     # -- iteration -----------------------------------------------------------

@@ -6,7 +6,8 @@ from typing import Any, Dict, Optional, Tuple
 
 import torch
 
-from .codec import AMO_BQ_PRESETS, dequantize_int8_amo_bq, quantize_int8_amo_bq
+from .codec import (AMO_BQ_PRESETS, dequantize_int8_amo_bq, dequantize_int8_g32, quantize_int8_adaptive,
+                    quantize_int8_amo_bq, quantize_int8_g32)
 
 
 def estimate_compression(shape: Tuple[int, ...], group_size: int = 32, amo_bq: bool = True) -> Dict[str, Any]:
@@ -27,17 +28,20 @@ def estimate_compression(shape: Tuple[int, ...], group_size: int = 32, amo_bq: b
 
 
 def compress(x: torch.Tensor, mode: str = "balanced", group_size: int = 32):
-    """AMO-BQ compress -> ``(q, scales, zero_points, shape)``."""
+    """AMO-BQ compress -> ``(q, scales, zero_points, shape)``; modes ``"sym"`` / ``"adaptive"`` return the
+    symmetric codec's ``(q, scales, shape)`` as the reference does (utils.py:125-139)."""
     if mode in AMO_BQ_PRESETS:
         return quantize_int8_amo_bq(x, group_size, mode=mode)
-    if mode in ("sym", "adaptive"):
-        raise NotImplementedError(f"mode {mode!r} (symmetric codec) is outside the B200 AMO-BQ path")
+    if mode == "sym":
+        return quantize_int8_g32(x, group_size)
+    if mode == "adaptive":
+        return quantize_int8_adaptive(x, group_size)
     raise ValueError(f"mode {mode!r} unknown, choose from {list(AMO_BQ_PRESETS.keys()) + ['sym', 'adaptive']}")
 
 
 def decompress(q: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, ...],
                zero_points: Optional[torch.Tensor] = None, group_size: int = 32) -> torch.Tensor:
-    """Decompress AMO-BQ codes to bf16 of ``shape``."""
+    """Decompress to bf16 of ``shape``: AMO-BQ codes when ``zero_points`` is given, else symmetric codes."""
     if zero_points is None:
-        raise NotImplementedError("symmetric decode (zero_points=None) is outside the B200 AMO-BQ path")
+        return dequantize_int8_g32(q, scales, shape, group_size)
     return dequantize_int8_amo_bq(q, scales, zero_points, shape, group_size)

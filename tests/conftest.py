@@ -21,6 +21,16 @@ def golden_small():
 
 
 @pytest.fixture(scope="session")
+def golden_extra():
+    return np.load(GOLDEN / "codec_extra.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_sym_rows():
+    return np.load(GOLDEN / "cache_sym_rows.npz")
+
+
+@pytest.fixture(scope="session")
 def golden_rows():
     return np.load(GOLDEN / "cache_rows.npz")
 

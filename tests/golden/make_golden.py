@@ -8,6 +8,10 @@ PyTorch path produces:
 * ``amo_small.npz``   inputs (bf16 / fp16 / fp32) and the full outputs
   (q, scale bits, zero points, decoded bf16 bits) for every AMO mode at
   G16/G32/G64, plus ragged sizes, non-finite values and constant groups.
+* ``codec_extra.npz``  the same for the symmetric codec (``quantize_int8_g32``,
+  ``quantize_int8_adaptive``, ``dequantize_int8_g32``) at G 8..128, and AMO-BQ at G8 / G128.
+* ``cache_sym_single/``, ``cache_sym_sharded/``, ``cache_sym_rows.npz``  tiny caches of the
+  symmetric codec (plain; adaptive with 3 shards) and the rows the reference's readers return.
 * ``config_digests.json``  SHA-256 digests of the reference outputs on the
   full-size seeded synthetic tensors of the benchmark configurations (the
   inputs are regenerated from the seed by ``tests/synth.py``; their digests are
@@ -46,15 +50,91 @@ def sha(a: np.ndarray) -> str:
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
+def make_codec_extra(tc):
+    from tensorcache.codec import dequantize_int8_g32, quantize_int8_adaptive, quantize_int8_g32
+
+    out = {}
+
+    def record_sym(name, x, adaptive, G):
+        q, s, _ = (quantize_int8_adaptive if adaptive else quantize_int8_g32)(x, G)
+        out[f"{name}/q"] = q.numpy().reshape(-1).copy()
+        out[f"{name}/s"] = bits(s)
+        out[f"{name}/rec"] = bits(dequantize_int8_g32(q, s, tuple(x.shape), G)) if q.numel() else np.zeros(0, np.uint16)
+
+    x = synth.config0_style(100, (6, 16, 96))  # the block of amo_small.npz
+    out["x_main"] = bits(x)
+    for G in (8, 16, 24, 32, 48, 64, 128):
+        for adaptive in (False, True):
+            record_sym(f"main/{'adaptive' if adaptive else 'sym'}/G{G}", x, adaptive, G)
+    for G in (8, 128):
+        for mode in ("balanced", "quality"):
+            q, s, zp, _ = tc.compress(x, mode, G)
+            out[f"main/{mode}/G{G}/q"] = q.numpy().reshape(-1).copy()
+            out[f"main/{mode}/G{G}/s"] = bits(s)
+            out[f"main/{mode}/G{G}/zp"] = zp.numpy().reshape(-1).copy()
+            out[f"main/{mode}/G{G}/rec"] = bits(tc.decompress(q, s, tuple(x.shape), zp, G))
+    g = torch.Generator().manual_seed(101)
+    for numel in synth.EDGE_NUMELS:
+        xr = (torch.randn(numel, generator=g) * 2.5).to(torch.bfloat16)
+        out[f"x_ragged{numel}"] = bits(xr)
+        for adaptive in (False, True):
+            for G in (16, 32, 24):
+                record_sym(f"ragged{numel}/{'adaptive' if adaptive else 'sym'}/G{G}", xr, adaptive, G)
+    xe = synth.edge_values()
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16"), (torch.float32, "f32")):
+        for adaptive in (False, True):
+            for G in (16, 32, 64):
+                record_sym(f"edge_{tag}/{'adaptive' if adaptive else 'sym'}/G{G}", xe.to(dt), adaptive, G)
+    out["mult/adaptive"] = torch.linspace(0.90, 1.05, 31).numpy().copy()
+    np.savez_compressed("codec_extra.npz", **out)
+    print("codec_extra.npz", os.path.getsize("codec_extra.npz"), "bytes,", len(out), "arrays")
+
+
+def make_sym_caches(tc):
+    """Caches of the symmetric codec written by the reference's writer, and what its readers return."""
+    from tensorcache.codec import dequantize_int8_g32
+
+    rows = {}
+    for sub in ("cache_sym_single", "cache_sym_sharded"):
+        shutil.rmtree(sub, ignore_errors=True)
+        os.makedirs(sub)
+    feats = synth.config0_style(102, (7, 6, 64))  # the samples of cache_single / cache_sharded
+    rows["features"] = bits(feats)
+    w = tc.FeatureCacheWriter("cache_sym_single/feat", 7, 6, 64, group_size=32)
+    w.append(feats[:3]); w.append(feats[3]); w.append(feats[4:]); w.close()
+    w = tc.FeatureCacheWriter("cache_sym_sharded/feat", 7, 6, 64, group_size=16, adaptive=True, num_shards=3)
+    w.append(feats); w.close()
+    for sub in ("cache_sym_single", "cache_sym_sharded"):
+        ds = tc.FeatureCacheDataset(f"{sub}/feat")
+        for i in range(len(ds)):
+            q, s = ds[i]
+            rows[f"{sub}/{i}/q"] = q.numpy().copy()
+            rows[f"{sub}/{i}/s"] = bits(s)
+            rows[f"{sub}/{i}/rec"] = bits(dequantize_int8_g32(q, s, (6, 64), ds.group_size))
+        ds.close()
+    st = tc.ZeroCopyTensorStreamer("cache_sym_sharded/feat", batch_size=2, device="cpu", shuffle=False, rank=1, world_size=3)
+    rows["cache_sym_sharded/rank1_of_3/num_samples"] = np.array([st.num_samples])
+    rows["cache_sym_sharded/rank1_of_3/rec"] = np.concatenate([bits(b) for b in st])
+    st.close()
+    np.savez_compressed("cache_sym_rows.npz", **rows)
+    print("cache_sym_rows.npz", len(rows), "arrays")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
     ap.add_argument("--skip-large", action="store_true")
+    ap.add_argument("--only-codec-extra", action="store_true",
+                    help="regenerate codec_extra.npz and the symmetric-codec caches, nothing else")
     a = ap.parse_args()
     sys.path.insert(0, str(Path(a.reference) / "src"))
     import tensorcache as tc
 
     os.chdir(HERE)
+    make_codec_extra(tc)
+    make_sym_caches(tc)
+    if a.only_codec_extra:
+        return
     small = {}
 
     def record(name, x, mode, G, **kw):

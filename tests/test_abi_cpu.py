@@ -37,8 +37,9 @@ def test_argument_validation_happens_before_any_device_work(built_lib):
 
     L = built_lib
     assert L.tcb_decompress_amo(None, None, None, None, 0, 32, None) == _lib.TCB_OK            # empty is fine
-    assert L.tcb_decompress_amo(None, None, None, None, 10, 24, None) == _lib.ERR_GROUP_SIZE
-    assert b"group_size 24" in L.tcb_last_error()
+    assert L.tcb_decompress_amo(None, None, None, None, 10, 20, None) == _lib.ERR_GROUP_SIZE
+    assert b"group_size 20" in L.tcb_last_error()
+    assert L.tcb_decompress_amo(None, None, None, None, 10, 24, None) == _lib.ERR_BAD_ARG       # 24 is a group size; nulls
     assert L.tcb_decompress_amo(None, None, None, None, -1, 32, None) == _lib.ERR_BAD_ARG
     assert L.tcb_decompress_amo(None, None, None, None, 10, 32, None) == _lib.ERR_BAD_ARG       # null pointers
     m = (ctypes.c_float * 4)(1, 1, 1, 1)
@@ -46,7 +47,15 @@ def test_argument_validation_happens_before_any_device_work(built_lib):
     assert L.tcb_compress_amo(None, 0, 10, 32, m, 65, None, None, None, None) == _lib.ERR_TOO_LARGE
     assert L.tcb_compress_amo(None, 0, 10, 32, None, 4, None, None, None, None) == _lib.ERR_BAD_ARG
     assert L.tcb_compress_amo(None, 7, 10, 32, m, 4, None, None, None, None) == _lib.ERR_BAD_ARG  # dtype
-    assert L.tcb_compress_amo_quality(None, 0, 10, 48, None, None, None, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_compress_amo_quality(None, 0, 10, 40, None, None, None, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_compress_sym(None, 0, 10, 32, m, 65, None, None, None) == _lib.ERR_TOO_LARGE
+    assert L.tcb_compress_sym(None, 0, 10, 32, None, 4, None, None, None) == _lib.ERR_BAD_ARG     # table missing
+    assert L.tcb_compress_sym(None, 0, 10, 12, None, 0, None, None, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_compress_sym(None, 0, 0, 32, None, 0, None, None, None) == _lib.TCB_OK
+    assert L.tcb_decompress_sym(None, None, None, 0, 32, None) == _lib.TCB_OK
+    assert L.tcb_decompress_sym(None, None, None, 10, 32, None) == _lib.ERR_BAD_ARG
+    assert L.tcb_decompress_sym(None, None, None, 10, 7, None) == _lib.ERR_GROUP_SIZE
+    assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 128, 24, 1, None) == _lib.ERR_GROUP_SIZE
     assert L.tcb_compress_amo_quality(None, 0, 0, 16, None, None, None, None) == _lib.TCB_OK
     assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 100, 32, 1, None) == _lib.ERR_BAD_ARG  # K % 64
     assert L.tcb_fused_dequant_linear(None, None, None, None, None, None, 8, 8, 128, 32, 1, None) == _lib.ERR_BAD_ARG  # nulls

@@ -157,3 +157,68 @@ def test_resident_shard_mode_reads_the_same_batches(tmp_path, golden_rows):
         np.random.seed(6)
         got = bits(torch.cat([b.clone() for b in st])).reshape(100, -1)
         assert np.array_equal(got, want[200:][st.indices])
+
+
+# ---------------------------------------------------------- caches of the symmetric codec
+
+@pytest.mark.parametrize("sub,kw", [("cache_sym_single", dict(group_size=32)),
+                                    ("cache_sym_sharded", dict(group_size=16, adaptive=True, num_shards=3))])
+def test_symmetric_writer_output_is_byte_identical_with_the_reference_writer(tmp_path, golden_sym_rows, sub, kw):
+    feats = from_bits(golden_sym_rows["features"]).view(7, 6, 64)
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 7, 6, 64, **kw)
+    w.append(feats[:3].to(DEV)); w.append(feats[3]); w.append(feats[4:])
+    w.close()
+    assert not list(tmp_path.glob("*_zp.bin"))
+    for ref_file in sorted((GOLDEN / sub).iterdir()):
+        mine = tmp_path / ref_file.name
+        assert mine.exists(), ref_file.name
+        if ref_file.suffix == ".bin":
+            assert mine.read_bytes() == ref_file.read_bytes(), ref_file.name
+        else:
+            a, b = json.loads(mine.read_text()), json.loads(ref_file.read_text())
+            for k in ("shard_prefixes", "shard_metas"):
+                a.pop(k, None), b.pop(k, None)
+            assert a == b, ref_file.name
+
+
+@pytest.mark.parametrize("sub", ["cache_sym_single", "cache_sym_sharded"])
+def test_readers_on_reference_written_symmetric_caches(golden_sym_rows, sub):
+    want = np.concatenate([golden_sym_rows[f"{sub}/{i}/rec"] for i in range(7)])
+    prefix = GOLDEN / sub / "feat"
+    for kw in (dict(), dict(low_vram=True), dict(pin_shard=True)):
+        with tc.ZeroCopyTensorStreamer(prefix, batch_size=2, device=DEV, shuffle=False, **kw) as st:
+            assert not st.amo_bq
+            for _ in range(2):
+                assert np.array_equal(bits(torch.cat([b.clone() for b in st])), want), kw
+    np.random.seed(4)
+    with tc.ZeroCopyTensorStreamer(prefix, batch_size=3, device=DEV, shuffle=True) as st:
+        got = torch.cat([b.clone() for b in st])
+        assert np.array_equal(bits(got).reshape(7, -1), want.reshape(7, -1)[st.indices])
+    ds = tc.FeatureCacheDataset(prefix, auto_dequant_device=DEV)
+    assert np.array_equal(bits(ds[2]), golden_sym_rows[f"{sub}/2/rec"])
+    got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=4, shuffle=False, device=DEV)])
+    assert np.array_equal(bits(got), want)
+    raw = list(ds.iter_batches(batch_size=4, shuffle=False, device=DEV, dequantize=False))
+    assert len(raw) == 2 and len(raw[0]) == 2 and raw[0][0].dtype == torch.int8
+    rec = tc.decompress(torch.cat([r[0] for r in raw]), torch.cat([r[1] for r in raw]), (7, 6, 64), None, ds.group_size)
+    assert np.array_equal(bits(rec), want)
+    ds.close()
+    if sub == "cache_sym_sharded":
+        with tc.ZeroCopyTensorStreamer(prefix, batch_size=2, device=DEV, shuffle=False, rank=1, world_size=3) as st:
+            assert np.array_equal(bits(torch.cat([b.clone() for b in st])), golden_sym_rows["cache_sym_sharded/rank1_of_3/rec"])
+
+
+def test_larger_symmetric_cache_round_trip(tmp_path):
+    """2 shards x 150 samples of [32, 256], adaptive codec: staging and resident paths, contiguous and shuffled."""
+    x = synth.config0_style(42, (300, 32, 256))
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 300, 32, 256, group_size=32, adaptive=True, num_shards=2)
+    w.append(x[:170].to(DEV)); w.append(x[170:]); w.close()
+    q, s, _ = tc.compress(x.to(DEV), "adaptive", 32)
+    want = bits(tc.decompress(q, s, (300, 32, 256), None, 32)).reshape(300, -1)
+    for pin in (False, True):
+        with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False, pin_shard=pin) as st:
+            assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(300, -1), want)
+            st.shuffle = True
+            np.random.seed(8)
+            got = bits(torch.cat([b.clone() for b in st])).reshape(300, -1)
+            assert np.array_equal(got, want[st.indices])

@@ -30,10 +30,12 @@ def test_api_surface_and_errors():
         tc.BlockwiseInt8Codec(adaptive=True, amo_bq=True)
     with pytest.raises(ValueError, match="unknown"):
         tc.compress(torch.zeros(4), mode="nope")
-    with pytest.raises(NotImplementedError):
-        tc.compress(torch.zeros(4), mode="sym")
     with pytest.raises(ValueError):
-        tc.quantize_int8_amo_bq(torch.zeros(64), group_size=24)
+        tc.quantize_int8_amo_bq(torch.zeros(64), group_size=20)
+    with pytest.raises(ValueError):
+        tc.quantize_int8_g32(torch.zeros(64), group_size=12)
+    assert repr(tc.BlockwiseInt8Codec(32)) == "BlockwiseInt8Codec(G=32, sym 1:1.88x)"
+    assert repr(tc.BlockwiseInt8Codec(32, adaptive=True)) == "BlockwiseInt8Codec(G=32, adaptive 0.90-1.05 1:1.88x)"
     e = tc.estimate_compression((16, 446, 768), 32)
     assert e["bytes_per_elem"] == 1.09375 and e["num_blocks"] == 171264
 
@@ -79,6 +81,22 @@ def test_reads_caches_written_by_the_reference(golden_rows, sub):
     ds.close()
 
 
+@pytest.mark.parametrize("sub", ["cache_sym_single", "cache_sym_sharded"])
+def test_reads_symmetric_caches_written_by_the_reference(golden_sym_rows, sub):
+    ds = tc.FeatureCacheDataset(GOLDEN / sub / "feat")
+    assert len(ds) == 7 and not ds.amo_bq and ds.group_size == (32 if sub == "cache_sym_single" else 16)
+    for i in range(7):
+        row = ds[i]
+        assert len(row) == 2 and row[0].dtype == torch.int8 and row[1].dtype == torch.bfloat16
+        assert np.array_equal(row[0].numpy(), golden_sym_rows[f"{sub}/{i}/q"])
+        assert np.array_equal(bits(row[1]), golden_sym_rows[f"{sub}/{i}/s"])
+    ds.close()
+    st = tc.ZeroCopyTensorStreamer(GOLDEN / "cache_sym_sharded" / "feat", batch_size=2, device="cpu", shuffle=False,
+                                   rank=1, world_size=3)
+    assert st.num_samples == int(golden_sym_rows["cache_sym_sharded/rank1_of_3/num_samples"][0]) and not st.amo_bq
+    st.close()
+
+
 def test_streamer_host_side_matches_reference_mapping(golden_rows):
     st = tc.ZeroCopyTensorStreamer(GOLDEN / "cache_sharded" / "feat", batch_size=2, device="cpu", shuffle=False,
                                    rank=1, world_size=3)
@@ -108,11 +126,6 @@ def test_truncated_and_missing_files_are_reported(tmp_path):
     os.remove(tmp_path / "feat_zp.bin")
     with pytest.raises((FileNotFoundError, ValueError)):
         tc.FeatureCacheDataset(tmp_path / "feat")
-    meta = json.loads((GOLDEN / "cache_single" / "feat_meta.json").read_text())
-    meta["amo_bq"] = False
-    (tmp_path / "feat_meta.json").write_text(json.dumps(meta))
-    with pytest.raises(NotImplementedError):
-        tc.FeatureCacheDataset(tmp_path / "feat")
 
 
 def test_writer_argument_checks(tmp_path):
@@ -122,8 +135,8 @@ def test_writer_argument_checks(tmp_path):
         tc.FeatureCacheWriter(tmp_path / "a", 4, 6, 64, amo_bq=True, quant_bits=4)
     with pytest.raises(ValueError):
         tc.FeatureCacheWriter(tmp_path / "a", 4, 6, 64, amo_bq=True, amo_mode="nope")
-    with pytest.raises(NotImplementedError):
-        tc.FeatureCacheWriter(tmp_path / "a", 4, 6, 64, amo_bq=False)
+    with pytest.raises(ValueError):
+        tc.FeatureCacheWriter(tmp_path / "a", 4, 6, 64, adaptive=True, amo_bq=True)
     with pytest.raises(FileNotFoundError):
         tc.FeatureCacheWriter.open_append(tmp_path / "missing", 3)
 

@@ -32,6 +32,39 @@ def test_other_group_sizes(golden_small, mode, G):
     _check(golden_small, f"main/{mode}/G{G}", golden_small["x_main"], mode, G)
 
 
+@pytest.mark.parametrize("G", [8, 128])
+@pytest.mark.parametrize("mode", ["balanced", "quality"])
+def test_smallest_and_largest_group_size(golden_extra, mode, G):
+    _check(golden_extra, f"main/{mode}/G{G}", golden_extra["x_main"], mode, G)
+
+
+def _check_sym(g, name, x, adaptive, G):
+    q, s = orc.compress_sym(x, G, adaptive)
+    assert np.array_equal(q, g[f"{name}/q"]), f"{name}: codes"
+    assert np.array_equal(s, g[f"{name}/s"]), f"{name}: scales"
+    assert np.array_equal(orc.decompress_sym(q, s, G), g[f"{name}/rec"]), f"{name}: decode"
+
+
+@pytest.mark.parametrize("kind", ["sym", "adaptive"])
+@pytest.mark.parametrize("G", [8, 16, 24, 32, 48, 64, 128])
+def test_symmetric_codec_main_block(golden_extra, kind, G):
+    _check_sym(golden_extra, f"main/{kind}/G{G}", golden_extra["x_main"], kind == "adaptive", G)
+
+
+@pytest.mark.parametrize("kind", ["sym", "adaptive"])
+def test_symmetric_codec_ragged_and_nonfinite(golden_extra, kind):
+    for numel in synth.EDGE_NUMELS:
+        for G in (16, 32, 24):
+            _check_sym(golden_extra, f"ragged{numel}/{kind}/G{G}", golden_extra[f"x_ragged{numel}"], kind == "adaptive", G)
+    xe = synth.edge_values()
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16"), (torch.float32, "f32")):
+        xx = xe.to(dt)
+        xin = bits(xx) if dt == torch.bfloat16 else xx.numpy()
+        for G in (16, 32, 64):
+            _check_sym(golden_extra, f"edge_{tag}/{kind}/G{G}", xin, kind == "adaptive", G)
+    assert np.array_equal(orc.linspace_multipliers(0.90, 1.05, 31), golden_extra["mult/adaptive"])
+
+
 @pytest.mark.parametrize("numel", synth.EDGE_NUMELS)
 def test_ragged_sizes(golden_small, numel):
     for mode in ("balanced", "quality"):
