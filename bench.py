@@ -283,7 +283,9 @@ def tensor_peak():
 def run_other_workload(args):
     """Single-GPU timings of the other kernels of the path (not the headline line):
     fused_linear: X [8192,4096] bf16 x AMO-BQ balanced G32 weight [14336,4096]  -> TFLOP/s
-    compress:     bf16 [256,1024,1024] Student-t(4) x lognormal channel scale   -> Gvalues/s"""
+    compress:     bf16 [256,1024,1024] Student-t(4) x lognormal channel scale   -> Gvalues/s
+                  (--mode: an AMO-BQ preset, or sym / adaptive for the symmetric codec)
+    decode_any:   decode of [128,446,768] random codes at --group-size, AMO-BQ or (--mode sym) symmetric -> GB/s"""
     import tensorcache_b200 as tc
     from tensorcache_b200.fused_linear import check_device_status
 
@@ -301,6 +303,29 @@ def run_other_workload(args):
         fn = lambda: tc.fused_dequant_matmul(x, wq, ws, wzp, None, args.group_size)
         work, unit, metric = 2.0 * M * N * K / 1e12, "TFLOP/s", "fused_dequant_linear_throughput"
         cfg = {"workload": f"FusedDequantLinear X[{M},{K}] bf16 x AMO-BQ balanced G{args.group_size} W[{N},{K}] -> bf16 [{M},{N}]"}
+    elif args.workload == "decode_any":
+        g = args.group_size
+        numel = 128 * 446 * 768 // g * g
+        sym = args.mode in ("sym", "adaptive")
+        sets = []
+        for k in range(4):   # rotate 4 x 136 MB so that no launch finds its inputs in L2
+            q = torch.randint(0, 256, (numel,), generator=gen, device=device, dtype=torch.uint8)
+            sc = torch.exp(torch.rand(numel // g, generator=gen, device=device) * 6 - 8).to(torch.bfloat16)
+            zp = None if sym else torch.randint(0, 256, (numel // g,), generator=gen, device=device, dtype=torch.uint8)
+            sets.append((q.view(torch.int8) if sym else q, sc, zp, torch.empty(numel, dtype=torch.bfloat16, device=device)))
+        it = [0]
+
+        def fn():
+            q, sc, zp, out = sets[it[0] & 3]
+            it[0] += 1
+            if sym:
+                tc.dequantize_int8_g32(q, sc, (numel,), g, out_buffer=out)
+            else:
+                tc.dequantize_int8_amo_bq(q, sc, zp, (numel,), g, out_buffer=out)
+        bpv = 3.0 + (2.0 if sym else 3.0) / g
+        work, unit, metric = numel * bpv / 1e9, "GB/s", f"{'sym' if sym else 'amo_bq'}_g{g}_dequant_throughput"
+        cfg = {"workload": f"{'symmetric' if sym else 'AMO-BQ'} G{g} decode of {numel} codes into a preallocated bf16 buffer",
+               "algorithmic_bytes_per_value": bpv, "l2": "4 rotating buffer sets of 136 MB each"}
     else:
         B, R, C = (int(v) for v in args.shape.split(",")) if args.shape else (256, 1024, 1024)
         ch = torch.exp(torch.randn(C, generator=gen, device=device))
@@ -314,7 +339,7 @@ def run_other_workload(args):
         fn = lambda: tc.compress(x, args.mode, args.group_size)
         work, unit, metric = x.numel() / 1e9, "Gvalues/s", f"amo_bq_compress_{args.mode}_g{args.group_size}_throughput"
         cfg = {"workload": f"AMO-BQ compress mode={args.mode} G{args.group_size} of bf16 [{B},{R},{C}]",
-               "algorithmic_bytes_per_value": 3.0 + 3.0 / args.group_size}
+               "algorithmic_bytes_per_value": 3.0 + (2.0 if args.mode in ("sym", "adaptive") else 3.0) / args.group_size}
     for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize(device)
@@ -338,9 +363,14 @@ def run_other_workload(args):
         line["dtype"] = "bf16 operands (dequantised in-kernel), fp32 accumulate"
         line["roofline"] = {"bound": "tensor", "achieved": value, "peak": sustained, "unit": "TFLOP/s", "frac": value / sustained,
                             "frac_of_burst": value / burst, "peak_kind": kind, "traffic": None}
+    elif args.workload == "decode_any":
+        hbm, kind = peaks()
+        line["dtype"] = "u8/i8 -> bf16 (fp32 arithmetic)"
+        line["roofline"] = {"bound": "hbm", "achieved": value, "peak": hbm, "unit": "GB/s", "frac": value / hbm, "peak_kind": kind,
+                            "traffic": None}
     else:
         hbm, kind = peaks()
-        gbs = value * (3.0 + 3.0 / args.group_size)
+        gbs = value * cfg["algorithmic_bytes_per_value"]
         line["dtype"] = "fp32 (IEEE div / rint, no FMA)"
         line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_kind": kind,
                             "traffic": None, "note": "the encoder is ALU-bound (one IEEE division and ~10 dependent fp32 operations "
@@ -359,10 +389,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed decodes one by one instead of replaying CUDA graphs")
     ap.add_argument("--decode-only", action="store_true", help="skip the streamer / e2e leg (for profiler captures)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "fused_linear", "compress"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "fused_linear", "compress", "decode_any"],
                     help="decode (default) is the headline metric; the other two time the remaining kernels of the path")
     ap.add_argument("--shape", default="", help="fused_linear: M,N,K; compress: B,R,C (defaults: the benchmark configurations)")
-    ap.add_argument("--mode", default="balanced", help="compress: AMO-BQ mode")
+    ap.add_argument("--mode", default="balanced", help="compress: AMO-BQ mode, or sym / adaptive; decode_any: sym selects the symmetric codec")
     ap.add_argument("--group-size", type=int, default=G)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -434,6 +434,179 @@ compress_sym_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, Can
     }
 }
 
+// Plain symmetric codec (no scale search) as a streaming kernel.  One pass over the data, so it is
+// bound by HBM (2 bytes read, 1 + 2/G written per bf16 value), not by arithmetic, and is laid out
+// like the decoder: every thread owns 16 consecutive values (one 256-bit load for 16-bit inputs, two
+// for fp32), G/16 neighbouring lanes form a group and combine their max|x| with xor-shuffles, and
+// each thread writes its 16 codes with one 128-bit store.  x / scale is the exact IEEE quotient, built
+// from the group's reciprocal and two FMAs per value (no division, no fallback path: with bf16 inputs
+// and a bf16 scale the quotient lands exactly on k + 0.5 for a large share of the values, so a
+// "rare boundary case" design does not work here); rounding to nearest-even and the conversion to
+// int8 come from adding 1.5 * 2^23, whose low mantissa byte is the two's-complement code.
+// Covers G in {16, 32, 64, 128}, whole groups, x 32-byte and q 16-byte aligned; everything else
+// (other G, ragged tail, odd alignment, the adaptive search) runs on compress_sym_kernel.
+constexpr int kSymUnroll = 2;
+
+// Loads 16 consecutive values as fp32 and reports whether any of them is NaN / Inf.  For the 16-bit
+// types the test runs on the packed words: an exponent field of all ones carries into the bit above
+// it when one unit of the exponent is added.
+template <typename T>
+__device__ __forceinline__ bool load16(const T* __restrict__ p, float (&v)[16]);
+
+__device__ __forceinline__ void ldg_stream_v8(const void* p, uint32_t (&w)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+
+template <>
+__device__ __forceinline__ bool load16<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8], flags = 0;
+    ldg_stream_v8(p, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        flags |= ((w[k] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+    return flags != 0;
+}
+
+template <>
+__device__ __forceinline__ bool load16<__half>(const __half* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8], flags = 0;
+    ldg_stream_v8(p, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        flags |= ((w[k] & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+    return flags != 0;
+}
+
+template <>
+__device__ __forceinline__ bool load16<float>(const float* __restrict__ p, float (&v)[16]) {
+    uint32_t w[8];
+    bool nonfinite = false;
+    ldg_stream_v8(p, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        nonfinite |= (w[k] << 1) >= 0xff000000u;
+        v[k] = __uint_as_float(w[k]);
+    }
+    ldg_stream_v8(p + 8, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        nonfinite |= (w[k] << 1) >= 0xff000000u;
+        v[8 + k] = __uint_as_float(w[k]);
+    }
+    return nonfinite;
+}
+
+template <int LPG, typename T>  // LPG = lanes per group = G / 16
+__global__ void __launch_bounds__(kThreads, 3)
+compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __restrict__ q, uint16_t* __restrict__ scales) {
+    // every block owns a contiguous range of 16-value units that starts and ends on a multiple of 8 units
+    // (LPG divides 8), so no group is split between blocks or between warps
+    const int64_t octs = units >> 3;
+    const int64_t begin = (octs * blockIdx.x / gridDim.x) << 3;
+    const int64_t end = blockIdx.x + 1 == gridDim.x ? units : (octs * (blockIdx.x + 1) / gridDim.x) << 3;
+    const float magic = 12582912.0f;  // 1.5 * 2^23
+
+    // the trip count is uniform across the block so that the shuffles always run with full warps
+    for (int64_t u0 = begin; u0 < end; u0 += int64_t(kThreads) * kSymUnroll) {
+        float v[kSymUnroll][16];
+        bool live[kSymUnroll], nonfinite[kSymUnroll];
+#pragma unroll
+        for (int k = 0; k < kSymUnroll; ++k) {
+            const int64_t u = u0 + int64_t(k) * kThreads + threadIdx.x;
+            live[k] = u < end;
+            nonfinite[k] = false;
+            if (live[k]) {
+                nonfinite[k] = load16<T>(x + (u << 4), v[k]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[k][i] = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kSymUnroll; ++k) {
+            const int64_t u = u0 + int64_t(k) * kThreads + threadIdx.x;
+            if (nonfinite[k]) {  // rare: NaN / Inf count as 0 and get code 0
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (!finite_f32(v[k][i])) v[k][i] = 0.0f;
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[k][i]));
+#pragma unroll
+            for (int off = 1; off < LPG; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const float s0 = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+            const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(s0));
+            const float sf = __uint_as_float(uint32_t(sbits) << 16);
+            const float rcp = __frcp_rn(sf);
+            // The IEEE quotient x / sf without a division per value: with r = rn(1 / sf) and t = rn(x * r),
+            // the residual x - t * sf is exact in one FMA and rn(t + residual * r) is the correctly rounded
+            // quotient (Markstein's correction step, the same one a division routine ends with; sf has an
+            // 8-bit significand, far from the all-ones case that step excludes).  Where the residual would
+            // underflow the quotient is far below 0.5 and rounds to code 0 either way.
+            // |x| <= amax and sf >= (amax / 127) (1 - 2^-9), so |x / sf| < 127.26: the reference's clamp to
+            // [-128, 127] never binds and is left out.  Adding 1.5 * 2^23 rounds to nearest-even.
+            uint32_t code[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float t = __fmul_rn(v[k][i], rcp);
+                const float quot = __fmaf_rn(__fmaf_rn(-t, sf, v[k][i]), rcp, t);
+                code[i] = __float_as_uint(__fadd_rn(quot, magic));
+            }
+            if (live[k]) {
+                uint4 o;
+                o.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+                o.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+                o.z = __byte_perm(__byte_perm(code[8], code[9], 0x0040), __byte_perm(code[10], code[11], 0x0040), 0x5410);
+                o.w = __byte_perm(__byte_perm(code[12], code[13], 0x0040), __byte_perm(code[14], code[15], 0x0040), 0x5410);
+                __stcs(reinterpret_cast<uint4*>(q + (u << 4)), o);  // streamed once: evict-first
+                if ((threadIdx.x & (LPG - 1)) == 0) scales[u / LPG] = sbits;
+            }
+        }
+    }
+}
+
+template <int LPG, typename T>
+cudaError_t launch_sym_stream(const void* x, int64_t groups, uint8_t* q, uint16_t* scales, cudaStream_t st) {
+    static int blocks_cache[64] = {0};
+    int dev = 0;
+    int resident = tcb::sm_count() * 4;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+        if (blocks_cache[dev] == 0) {
+            int per_sm = 0;
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, compress_sym_stream_kernel<LPG, T>, kThreads, 0) != cudaSuccess ||
+                per_sm < 1)
+                per_sm = 4;
+            blocks_cache[dev] = per_sm * tcb::sm_count();
+        }
+        resident = blocks_cache[dev];
+    }
+    const int64_t units = groups * LPG;
+    int64_t grid = resident;  // one wave; small inputs get fewer, fuller blocks
+    if (grid * kThreads > units) grid = (units + kThreads - 1) / kThreads;
+    if (grid < 1) grid = 1;
+    compress_sym_stream_kernel<LPG, T><<<unsigned(grid), kThreads, 0, st>>>(static_cast<const T*>(x), units, q, scales);
+    return cudaGetLastError();
+}
+
+template <int LPG>
+cudaError_t launch_sym_stream_typed(const void* x, int dtype, int64_t groups, uint8_t* q, uint16_t* scales, cudaStream_t st) {
+    switch (dtype) {
+    case TCB_DT_BF16: return launch_sym_stream<LPG, __nv_bfloat16>(x, groups, q, scales, st);
+    case TCB_DT_F16: return launch_sym_stream<LPG, __half>(x, groups, q, scales, st);
+    default: return launch_sym_stream<LPG, float>(x, groups, q, scales, st);
+    }
+}
+
 // -------------------------------------------------------------------- dispatch
 
 enum class Coder { Legacy, Quality, Sym };
@@ -481,11 +654,30 @@ int compress_common(const char* who, Coder coder, const void* x, int dtype, int6
     if (reinterpret_cast<uintptr_t>(x) % esz) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: x not aligned to its element size", who);
     if (reinterpret_cast<uintptr_t>(scales) & 1) return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales not 2-byte aligned", who);
 
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // plain symmetric codec: the whole groups go through the streaming kernel when the layout allows it
+    if (coder == Coder::Sym && tab->n == 0 && (group_size == 16 || group_size == 32 || group_size == 64 || group_size == 128) &&
+        reinterpret_cast<uintptr_t>(x) % 32 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0 && numel >= group_size) {
+        const int64_t whole = numel / group_size;
+        cudaError_t e;
+        switch (group_size) {
+        case 16: e = launch_sym_stream_typed<1>(x, dtype, whole, q, scales, st); break;
+        case 32: e = launch_sym_stream_typed<2>(x, dtype, whole, q, scales, st); break;
+        case 64: e = launch_sym_stream_typed<4>(x, dtype, whole, q, scales, st); break;
+        default: e = launch_sym_stream_typed<8>(x, dtype, whole, q, scales, st); break;
+        }
+        if (e != cudaSuccess) return tcb::cuda_fail(e, who);
+        const int64_t done = whole * group_size;
+        if (done == numel) return TCB_OK;
+        x = static_cast<const uint8_t*>(x) + done * esz;  // the ragged last group takes the general kernel
+        q += done;
+        scales += whole;
+        numel -= done;
+    }
     const int64_t ngroups = (numel + group_size - 1) / group_size;
     const int64_t blocks = (ngroups + kThreads / 4 - 1) / (kThreads / 4);
     const int64_t max_grid = int64_t(tcb::sm_count()) * 64;
     const int grid = int(blocks < max_grid ? blocks : max_grid);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     switch (group_size) {
     case 8: e = launch_g<8>(coder, x, dtype, numel, ngroups, tab, q, scales, zp, grid, st); break;

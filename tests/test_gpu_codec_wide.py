@@ -158,9 +158,36 @@ def test_encode_every_group_size_against_oracle(L, dev):
                     assert np.array_equal(a, b), (tag, G, mode, what, np.flatnonzero(a != b)[:5])
             for adaptive in (False, True):
                 want = orc.compress_sym(oarr, G, adaptive, nthreads=4)
-                got = abi_compress_sym(L, dev, arr, tag, G, adaptive_m if adaptive else None, x_off=1 if G == 48 else 0)
-                for a, b, what in zip(got, want, ("codes", "scales")):
-                    assert np.array_equal(a, b), (tag, G, "adaptive" if adaptive else "sym", what, np.flatnonzero(a != b)[:5])
+                # offsets: 0 and 16 elements keep the streaming kernel's alignment, 1 and 8 force the general kernel
+                for x_off in ((0, 1, 8, 16) if not adaptive else (1 if G == 48 else 0,)):
+                    got = abi_compress_sym(L, dev, arr, tag, G, adaptive_m if adaptive else None, x_off=x_off)
+                    for a, b, what in zip(got, want, ("codes", "scales")):
+                        assert np.array_equal(a, b), (tag, G, "adaptive" if adaptive else "sym", x_off, what, np.flatnonzero(a != b)[:5])
+
+
+def test_symmetric_streaming_encoder_boundary_cases(L, dev):
+    """Values placed on and next to the rounding boundaries k + 0.5 of x / scale, where the reciprocal
+    shortcut must hand over to the exact division, and groups whose maximum makes the bf16 scale round
+    up or down."""
+    from oracle import amo_oracle as orc
+
+    rng = np.random.default_rng(77)
+    n_groups = 16384
+    for G in (16, 32, 64, 128):
+        amax = np.exp(rng.uniform(-60, 60, n_groups)).astype(np.float32)
+        sf = torch.from_numpy(amax / np.float32(127.0)).to(torch.bfloat16).float().numpy()
+        k = rng.integers(-127, 127, (n_groups, G)).astype(np.float32) + 0.5
+        x = k * sf[:, None]                                   # x / sf is a half-integer up to rounding
+        ulps = rng.integers(-2, 3, x.shape)
+        x = (x.view(np.int32) + ulps).view(np.float32)        # ... and its neighbours
+        x[:, 0] = amax                                        # pin the group maximum
+        x = np.clip(x, -amax[:, None], amax[:, None]).astype(np.float32).reshape(-1)
+        xb = bits(torch.from_numpy(x).to(torch.bfloat16))     # bf16 values over a bf16 scale: exact ties are common
+        for tag, arr in (("f32", x), ("bf16", xb)):
+            want = orc.compress_sym(arr, G, False, nthreads=4)
+            got = abi_compress_sym(L, dev, arr, tag, G)
+            assert np.array_equal(got[1], want[1]), (G, tag, "scales")
+            assert np.array_equal(got[0], want[0]), (G, tag, np.flatnonzero(got[0] != want[0])[:8])
 
 
 def test_symmetric_benchmark_size_against_oracle(dev):
