@@ -55,6 +55,19 @@ __device__ __forceinline__ float quant_index(float x, float s, float r, float zp
     return k;
 }
 
+// The correctly rounded quotient x / s without a division, for a divisor whose significand is not
+// all ones (the scales of the quality search and of the symmetric codec are bf16 values: 8 bits).
+// With r = rn(1 / s) and t = rn(x * r), the residual x - t * s is exact in one FMA and
+// rn(t + residual * r) is the IEEE quotient (Markstein's correction step, the one a division routine
+// ends with).  The residual can only underflow where the quotient is far below 2^-20, which cannot
+// change the rounded code.  Needed, rather than the guard of quant_index, wherever values and scale
+// are both short: then x / s lands exactly on k + 0.5 for a large share of the values and a
+// "rare boundary" fallback would run all the time.
+__device__ __forceinline__ float exact_quotient(float x, float s, float r) {
+    const float t = __fmul_rn(x, r);
+    return __fmaf_rn(__fmaf_rn(-t, s, x), r, t);
+}
+
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 template <typename T>
@@ -320,22 +333,11 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
             const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
             const float rcp = __frcp_rn(s);
-            // rounded indices on the straight-line fast path, boundary cases redone afterwards (as in
-            // the legacy kernel), then the three-way code choice per value
-            float e[VPL], r[VPL];
-            bool doubtful = false;
+            // rounded index from the exact quotient (the scale is a bf16 value), then the three-way code choice
+            float e[VPL];
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) {
-                const float t = __fadd_rn(__fmul_rn(v[i], rcp), zp);
-                r[i] = rintf(t);
-                doubtful |= !(fabsf(__fsub_rn(t, r[i])) <= kBoundaryGuard);
-            }
-            if (doubtful) {
-#pragma unroll
-                for (int i = 0; i < VPL; ++i) r[i] = quant_index(v[i], s, rcp, zp);
-            }
-#pragma unroll
-            for (int i = 0; i < VPL; ++i) (void)quality_code(v[i], s, zp, r[i], e[i]);
+            for (int i = 0; i < VPL; ++i)
+                (void)quality_code(v[i], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)), e[i]);
             if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
                 for (int i = 0; i < VPL; ++i)
@@ -355,7 +357,7 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             float err;
-            const float qf = quality_code(v[i], best_s, best_zp, quant_index(v[i], best_s, best_rcp, best_zp), err);
+            const float qf = quality_code(v[i], best_s, best_zp, rintf(__fadd_rn(exact_quotient(v[i], best_s, best_rcp), best_zp)), err);
             codes[i] = ((finmask >> i) & 1u) ? uint8_t(qf) : zp8;
         }
         store_codes<G>(q, numel, base, j, out_aligned, codes);
@@ -548,19 +550,13 @@ compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __re
             const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(s0));
             const float sf = __uint_as_float(uint32_t(sbits) << 16);
             const float rcp = __frcp_rn(sf);
-            // The IEEE quotient x / sf without a division per value: with r = rn(1 / sf) and t = rn(x * r),
-            // the residual x - t * sf is exact in one FMA and rn(t + residual * r) is the correctly rounded
-            // quotient (Markstein's correction step, the same one a division routine ends with; sf has an
-            // 8-bit significand, far from the all-ones case that step excludes).  Where the residual would
-            // underflow the quotient is far below 0.5 and rounds to code 0 either way.
+            // x / sf is the exact IEEE quotient (exact_quotient: sf has an 8-bit significand).
             // |x| <= amax and sf >= (amax / 127) (1 - 2^-9), so |x / sf| < 127.26: the reference's clamp to
             // [-128, 127] never binds and is left out.  Adding 1.5 * 2^23 rounds to nearest-even.
             uint32_t code[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float t = __fmul_rn(v[k][i], rcp);
-                const float quot = __fmaf_rn(__fmaf_rn(-t, sf, v[k][i]), rcp, t);
-                code[i] = __float_as_uint(__fadd_rn(quot, magic));
+                code[i] = __float_as_uint(__fadd_rn(exact_quotient(v[k][i], sf, rcp), magic));
             }
             if (live[k]) {
                 uint4 o;
