@@ -449,66 +449,102 @@ compress_sym_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, Can
 // (other G, ragged tail, odd alignment, the adaptive search) runs on compress_sym_kernel.
 constexpr int kSymUnroll = 2;
 
-// Loads 16 consecutive values as fp32 and reports whether any of them is NaN / Inf.  For the 16-bit
-// types the test runs on the packed words: an exponent field of all ones carries into the bit above
-// it when one unit of the exponent is added.
+// Sixteen consecutive values in the registers they were loaded into (8 words for the 16-bit types,
+// 16 for fp32); they are widened to fp32 where they are used, twice, which is cheaper than holding
+// 16 floats per unit in flight: fewer registers, more resident warps, more loads in flight.
 template <typename T>
-__device__ __forceinline__ bool load16(const T* __restrict__ p, float (&v)[16]);
+struct Raw16;
 
-__device__ __forceinline__ void ldg_stream_v8(const void* p, uint32_t (&w)[8]) {
+__device__ __forceinline__ void ldg_stream_v8(const void* p, uint32_t* w) {
     asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
                  : "l"(p));
 }
 
 template <>
-__device__ __forceinline__ bool load16<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, float (&v)[16]) {
-    uint32_t w[8], flags = 0;
-    ldg_stream_v8(p, w);
+struct Raw16<__nv_bfloat16> {
+    static constexpr int kWords = 8;
+    uint32_t w[kWords];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { ldg_stream_v8(p, w); }
+    __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        flags |= ((w[k] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
-        v[2 * k] = __uint_as_float(w[k] << 16);
-        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    return flags != 0;
-}
+    // an exponent field of all ones carries into the bit above it when one unit of the exponent is added
+    __device__ __forceinline__ bool any_nonfinite() const {
+        uint32_t flags = 0;
+#pragma unroll
+        for (int k = 0; k < kWords; ++k) flags |= ((w[k] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
+        return flags != 0;
+    }
+    __device__ __forceinline__ void clean() {  // NaN / Inf -> 0
+#pragma unroll
+        for (int k = 0; k < kWords; ++k) {
+            if ((w[k] & 0x7f80u) == 0x7f80u) w[k] &= 0xffff0000u;
+            if ((w[k] & 0x7f800000u) == 0x7f800000u) w[k] &= 0x0000ffffu;
+        }
+    }
+    __device__ __forceinline__ float get(int i) const {
+        return __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));
+    }
+};
 
 template <>
-__device__ __forceinline__ bool load16<__half>(const __half* __restrict__ p, float (&v)[16]) {
-    uint32_t w[8], flags = 0;
-    ldg_stream_v8(p, w);
+struct Raw16<__half> {
+    static constexpr int kWords = 8;
+    uint32_t w[kWords];
+    __device__ __forceinline__ void load(const __half* p) { ldg_stream_v8(p, w); }
+    __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        flags |= ((w[k] & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-        v[2 * k] = f.x;
-        v[2 * k + 1] = f.y;
+        for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    return flags != 0;
-}
+    __device__ __forceinline__ bool any_nonfinite() const {
+        uint32_t flags = 0;
+#pragma unroll
+        for (int k = 0; k < kWords; ++k) flags |= ((w[k] & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
+        return flags != 0;
+    }
+    __device__ __forceinline__ void clean() {
+#pragma unroll
+        for (int k = 0; k < kWords; ++k) {
+            if ((w[k] & 0x7c00u) == 0x7c00u) w[k] &= 0xffff0000u;
+            if ((w[k] & 0x7c000000u) == 0x7c000000u) w[k] &= 0x0000ffffu;
+        }
+    }
+    __device__ __forceinline__ float get(int i) const {
+        const __half2 h = *reinterpret_cast<const __half2*>(&w[i >> 1]);
+        return (i & 1) ? __high2float(h) : __low2float(h);
+    }
+};
 
 template <>
-__device__ __forceinline__ bool load16<float>(const float* __restrict__ p, float (&v)[16]) {
-    uint32_t w[8];
-    bool nonfinite = false;
-    ldg_stream_v8(p, w);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        nonfinite |= (w[k] << 1) >= 0xff000000u;
-        v[k] = __uint_as_float(w[k]);
+struct Raw16<float> {
+    static constexpr int kWords = 16;
+    uint32_t w[kWords];
+    __device__ __forceinline__ void load(const float* p) {
+        ldg_stream_v8(p, w);
+        ldg_stream_v8(p + 8, w + 8);
     }
-    ldg_stream_v8(p + 8, w);
+    __device__ __forceinline__ void zero() {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        nonfinite |= (w[k] << 1) >= 0xff000000u;
-        v[8 + k] = __uint_as_float(w[k]);
+        for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    return nonfinite;
-}
+    __device__ __forceinline__ bool any_nonfinite() const {
+        bool nf = false;
+#pragma unroll
+        for (int k = 0; k < kWords; ++k) nf |= (w[k] << 1) >= 0xff000000u;
+        return nf;
+    }
+    __device__ __forceinline__ void clean() {
+#pragma unroll
+        for (int k = 0; k < kWords; ++k)
+            if ((w[k] << 1) >= 0xff000000u) w[k] = 0;
+    }
+    __device__ __forceinline__ float get(int i) const { return __uint_as_float(w[i]); }
+};
 
 template <int LPG, typename T>  // LPG = lanes per group = G / 16
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 5)
 compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __restrict__ q, uint16_t* __restrict__ scales) {
     // every block owns a contiguous range of 16-value units that starts and ends on a multiple of 8 units
     // (LPG divides 8), so no group is split between blocks or between warps
@@ -519,31 +555,22 @@ compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __re
 
     // the trip count is uniform across the block so that the shuffles always run with full warps
     for (int64_t u0 = begin; u0 < end; u0 += int64_t(kThreads) * kSymUnroll) {
-        float v[kSymUnroll][16];
-        bool live[kSymUnroll], nonfinite[kSymUnroll];
+        Raw16<T> raw[kSymUnroll];
+        bool live[kSymUnroll];
 #pragma unroll
         for (int k = 0; k < kSymUnroll; ++k) {
             const int64_t u = u0 + int64_t(k) * kThreads + threadIdx.x;
             live[k] = u < end;
-            nonfinite[k] = false;
-            if (live[k]) {
-                nonfinite[k] = load16<T>(x + (u << 4), v[k]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) v[k][i] = 0.0f;
-            }
+            if (live[k]) raw[k].load(x + (u << 4));
+            else raw[k].zero();
         }
 #pragma unroll
         for (int k = 0; k < kSymUnroll; ++k) {
             const int64_t u = u0 + int64_t(k) * kThreads + threadIdx.x;
-            if (nonfinite[k]) {  // rare: NaN / Inf count as 0 and get code 0
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (!finite_f32(v[k][i])) v[k][i] = 0.0f;
-            }
+            if (raw[k].any_nonfinite()) raw[k].clean();  // rare: NaN / Inf count as 0 and get code 0
             float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[k][i]));
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(raw[k].get(i)));
 #pragma unroll
             for (int off = 1; off < LPG; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             const float s0 = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
@@ -555,9 +582,8 @@ compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __re
             // [-128, 127] never binds and is left out.  Adding 1.5 * 2^23 rounds to nearest-even.
             uint32_t code[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                code[i] = __float_as_uint(__fadd_rn(exact_quotient(v[k][i], sf, rcp), magic));
-            }
+            for (int i = 0; i < 16; ++i)
+                code[i] = __float_as_uint(__fadd_rn(exact_quotient(raw[k].get(i), sf, rcp), magic));
             if (live[k]) {
                 uint4 o;
                 o.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
