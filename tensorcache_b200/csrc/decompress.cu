@@ -227,7 +227,71 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
     }
 }
 
-// Group sizes that are a multiple of 8 but not a power of two >= 16 (8, 24, 48): 8 codes per
+// Group sizes that are a multiple of 8 but not a power of two >= 16 (8, 24, 48), 32-byte aligned
+// pointers: the main kernel's data movement (32 codes per thread, one 256-bit load, two 256-bit
+// stores) with one scale / zero point per octet of codes, since a thread's four octets can belong to
+// up to four groups.  OPG = octets per group.
+template <int OPG, bool SYM>
+__global__ void __launch_bounds__(kThreads)
+decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zp,
+                         uint16_t* __restrict__ out, int64_t numel) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int64_t units = numel >> 5;
+    const int64_t begin = units * blockIdx.x / gridDim.x;
+    const int64_t end = units * (blockIdx.x + 1) / gridDim.x;
+
+    for (int64_t t0 = begin + threadIdx.x; t0 < end; t0 += int64_t(kThreads) * kUnroll32) {
+        uint32_t w[kUnroll32][8];
+        uint16_t sb[kUnroll32][4];
+        uint8_t zb[kUnroll32][4];
+#pragma unroll
+        for (int u = 0; u < kUnroll32; ++u) {
+            const int64_t t = t0 + int64_t(u) * kThreads;
+            if (t < end) {
+                ldg_stream_v8(q + (t << 5), w[u]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t g = (4 * t + j) / OPG;
+                    sb[u][j] = __ldg(scales + g);
+                    zb[u][j] = SYM ? uint8_t(128) : __ldg(zp + g);
+                }
+                if (SYM) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) w[u][k] ^= kSignFlip;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll32; ++u) {
+            const int64_t t = t0 + int64_t(u) * kThreads;
+            if (t < end) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t o[8];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float scale = bf16_bits_to_float(sb[u][2 * h + j]);
+                        const float zmagic = 8388608.0f + float(zb[u][2 * h + j]);
+                        convert_word(w[u][4 * h + 2 * j], zmagic, scale, o[4 * j], o[4 * j + 1]);
+                        convert_word(w[u][4 * h + 2 * j + 1], zmagic, scale, o[4 * j + 2], o[4 * j + 3]);
+                    }
+                    stg_stream_v8(out + (t << 5) + 16 * h, o);
+                }
+            }
+        }
+    }
+
+    const int tail = int(numel & 31);
+    if (blockIdx.x == 0 && threadIdx.x < tail) {
+        const int64_t i = (units << 5) + threadIdx.x;
+        const int64_t g = i / (8 * OPG);
+        out[i] = decode_one<SYM>(q[i], zp, g, scales[g]);
+    }
+}
+
+// The same group sizes with pointers that are not 32-byte aligned: 8 codes per
 // thread, one 64-bit load and one 128-bit store; OPG = octets per group.  Needs q 8-byte and out
 // 16-byte aligned.
 template <int OPG, bool SYM>
@@ -336,8 +400,10 @@ cudaError_t launch_aligned(const uint8_t* q, const uint16_t* s, const uint8_t* z
 }
 
 template <int OPG, bool SYM>
-cudaError_t launch_oct(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel, cudaStream_t st) {
-    static int cache[64] = {0};
+cudaError_t launch_oct(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel, bool aligned32,
+                       cudaStream_t st) {
+    static int cache[64] = {0}, cache32[64] = {0};
+    if (aligned32) return launch_one_wave(decompress_v8_oct_kernel<OPG, SYM>, cache32, numel >> 5, q, s, zp, out, numel, st);
     return launch_one_wave(decompress_oct_kernel<OPG, SYM>, cache, numel >> 3, reinterpret_cast<const uint2*>(q), s, zp, out,
                            numel, st);
 }
@@ -358,9 +424,9 @@ int launch_any(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint
     const bool aligned32 = ((qa | oa) & 31) == 0;
     cudaError_t e;
     switch (group_size) {
-    case 8: e = launch_oct<1, SYM>(q, scales, zp, out, numel, st); break;
-    case 24: e = launch_oct<3, SYM>(q, scales, zp, out, numel, st); break;
-    case 48: e = launch_oct<6, SYM>(q, scales, zp, out, numel, st); break;
+    case 8: e = launch_oct<1, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    case 24: e = launch_oct<3, SYM>(q, scales, zp, out, numel, aligned32, st); break;
+    case 48: e = launch_oct<6, SYM>(q, scales, zp, out, numel, aligned32, st); break;
     case 16: e = launch_aligned<4, SYM>(q, scales, zp, out, numel, aligned32, st); break;
     case 32: e = launch_aligned<5, SYM>(q, scales, zp, out, numel, aligned32, st); break;
     case 64: e = launch_aligned<6, SYM>(q, scales, zp, out, numel, aligned32, st); break;
