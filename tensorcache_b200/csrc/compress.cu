@@ -470,12 +470,12 @@ struct Raw16<__nv_bfloat16> {
 #pragma unroll
         for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    // an exponent field of all ones carries into the bit above it when one unit of the exponent is added
-    __device__ __forceinline__ bool any_nonfinite() const {
-        uint32_t flags = 0;
+    // max |x| over the 16 values, computed on the packed pairs; NaN if any value is NaN, Inf if any is Inf
+    __device__ __forceinline__ float amax_or_nonfinite() const {
+        __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]));
 #pragma unroll
-        for (int k = 0; k < kWords; ++k) flags |= ((w[k] & 0x7f807f80u) + 0x00800080u) & 0x80008000u;
-        return flags != 0;
+        for (int k = 1; k < kWords; ++k) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[k])));
+        return __bfloat162float(__hmax_nan(__low2bfloat16(m), __high2bfloat16(m)));
     }
     __device__ __forceinline__ void clean() {  // NaN / Inf -> 0
 #pragma unroll
@@ -498,11 +498,11 @@ struct Raw16<__half> {
 #pragma unroll
         for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    __device__ __forceinline__ bool any_nonfinite() const {
-        uint32_t flags = 0;
+    __device__ __forceinline__ float amax_or_nonfinite() const {
+        __half2 m = __habs2(*reinterpret_cast<const __half2*>(&w[0]));
 #pragma unroll
-        for (int k = 0; k < kWords; ++k) flags |= ((w[k] & 0x7c007c00u) + 0x04000400u) & 0x80008000u;
-        return flags != 0;
+        for (int k = 1; k < kWords; ++k) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __half2*>(&w[k])));
+        return __half2float(__hmax_nan(__low2half(m), __high2half(m)));
     }
     __device__ __forceinline__ void clean() {
 #pragma unroll
@@ -529,11 +529,12 @@ struct Raw16<float> {
 #pragma unroll
         for (int k = 0; k < kWords; ++k) w[k] = 0;
     }
-    __device__ __forceinline__ bool any_nonfinite() const {
-        bool nf = false;
+    // non-negative floats order like their bit patterns, and NaN / Inf patterns sort above every finite one
+    __device__ __forceinline__ float amax_or_nonfinite() const {
+        uint32_t m = 0;
 #pragma unroll
-        for (int k = 0; k < kWords; ++k) nf |= (w[k] << 1) >= 0xff000000u;
-        return nf;
+        for (int k = 0; k < kWords; ++k) m = max(m, w[k] & 0x7fffffffu);
+        return __uint_as_float(m);
     }
     __device__ __forceinline__ void clean() {
 #pragma unroll
@@ -567,10 +568,11 @@ compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __re
 #pragma unroll
         for (int k = 0; k < kSymUnroll; ++k) {
             const int64_t u = u0 + int64_t(k) * kThreads + threadIdx.x;
-            if (raw[k].any_nonfinite()) raw[k].clean();  // rare: NaN / Inf count as 0 and get code 0
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(raw[k].get(i)));
+            float amax = raw[k].amax_or_nonfinite();
+            if (!finite_f32(amax)) {  // rare: NaN / Inf count as 0 and get code 0
+                raw[k].clean();
+                amax = raw[k].amax_or_nonfinite();
+            }
 #pragma unroll
             for (int off = 1; off < LPG; off <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             const float s0 = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
