@@ -1,4 +1,4 @@
-"""One-line helpers with the reference's signatures (src/tensorcache/utils.py:22-44, 125-152)."""
+"""One-line helpers with the reference's signatures (src/tensorcache/utils.py:22-152)."""
 from __future__ import annotations
 
 import math
@@ -45,3 +45,58 @@ def decompress(q: torch.Tensor, scales: torch.Tensor, shape: Tuple[int, ...],
     if zero_points is None:
         return dequantize_int8_g32(q, scales, shape, group_size)
     return dequantize_int8_amo_bq(q, scales, zero_points, shape, group_size)
+
+
+def _rel_error_percent(x: torch.Tensor, rec: torch.Tensor) -> float:
+    xf = x.float()
+    return (torch.norm(xf - rec.float().to(xf.device)) / torch.norm(xf)).item() * 100
+
+
+def benchmark_tensor(x: torch.Tensor, group_size: int = 32, device: Optional[str] = None, verbose: bool = True,
+                     include_quality: bool = False) -> Dict[str, Any]:
+    """Relative error (percent) and encode latency of every codec mode on ``x``; the result dictionary has the
+    reference's keys (utils.py:46-103): ``sym_g32``, ``adaptive``, ``amo_<mode>`` -> ``{"rel_rmse%", "ms", ...}``.
+    ``quality`` is only tried when ``include_quality`` is set.  Latency is measured with CUDA events."""
+    if device:
+        x = x.to(device)
+
+    def timed(fn):
+        if not torch.cuda.is_available():
+            raise RuntimeError("tensorcache_b200 computes on a CUDA device only (no CPU fallback) and none is available")
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn()
+        stop.record()
+        stop.synchronize()
+        return out, start.elapsed_time(stop)
+
+    results: Dict[str, Any] = {}
+    for name, fn in (("sym_g32", quantize_int8_g32), ("adaptive", quantize_int8_adaptive)):
+        (q, s, shape), ms = timed(lambda: fn(x, group_size))
+        results[name] = {"rel_rmse%": _rel_error_percent(x, dequantize_int8_g32(q, s, shape, group_size)), "ms": ms}
+    modes = ["fast", "balanced", "accurate", "max"] + (["quality"] if include_quality else [])
+    for mode in modes:
+        (q, s, zp, shape), ms = timed(lambda: quantize_int8_amo_bq(x, group_size, mode=mode))
+        n, lo, hi = AMO_BQ_PRESETS[mode][:3]
+        results[f"amo_{mode}"] = {"rel_rmse%": _rel_error_percent(x, dequantize_int8_amo_bq(q, s, zp, shape, group_size)),
+                                  "ms": ms, "N": n, "lo": lo, "hi": hi}
+    if verbose:
+        print(f"tensorcache_b200 bench {tuple(x.shape)} {x.dtype} {x.device}")
+        for key, v in results.items():
+            label = f"sym_g{group_size}" if key == "sym_g32" else key
+            bpe = 1 + (3 if key.startswith("amo") else 2) / group_size
+            print(f"{label:14s} rel={v['rel_rmse%']:.4f}% ms={v['ms']:.3f} B/elem={bpe:.4f}")
+    return results
+
+
+def auto_select_mode(x: torch.Tensor, target_rmse: float = 0.5, group_size: int = 32, include_quality: bool = False) -> str:
+    """Cheapest AMO-BQ preset whose relative error (percent) meets ``target_rmse``; falls back to the same search at
+    G16 (returned as ``"G16_<mode>"``), then to the strongest preset -- the reference's policy (utils.py:106-122)."""
+    res = benchmark_tensor(x, group_size, verbose=False, include_quality=include_quality)
+    modes = ["fast", "balanced", "accurate", "max"] + (["quality"] if include_quality else [])
+    for mode in modes:
+        if res[f"amo_{mode}"]["rel_rmse%"] <= target_rmse:
+            return mode
+    if group_size > 16:
+        return f"G16_{auto_select_mode(x, target_rmse, 16, include_quality)}"
+    return "quality" if include_quality else "max"

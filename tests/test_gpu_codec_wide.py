@@ -232,3 +232,22 @@ def test_symmetric_python_api_contract(dev, golden_extra):
     y = lin(aq.view(64, 128), as_)
     ref = tc.dequantize_int8_g32(aq, as_, (64, 128), 32).float() @ lin.weight.float().t()
     assert (y.float() - ref).norm() / ref.norm() < 1e-2  # tolerance of the fused GEMM: rel. Frobenius <= 1e-2
+
+
+def test_benchmark_tensor_and_auto_select_mode(dev, golden_small, golden_extra):
+    import tensorcache_b200 as tc
+
+    x = from_bits(golden_small["x_main"]).reshape(6, 16, 96)
+    res = tc.benchmark_tensor(x.to(dev), 32, verbose=False, include_quality=True)
+    assert set(res) == {"sym_g32", "adaptive", "amo_fast", "amo_balanced", "amo_accurate", "amo_max", "amo_quality"}
+    xf = x.float().reshape(-1)
+    for key, g, name in (("amo_balanced", golden_small, "main/balanced/G32"), ("amo_quality", golden_small, "main/quality/G32"),
+                         ("sym_g32", golden_extra, "main/sym/G32"), ("adaptive", golden_extra, "main/adaptive/G32")):
+        rec = from_bits(g[f"{name}/rec"]).float()
+        want = (torch.norm(xf - rec) / torch.norm(xf)).item() * 100      # error of the reference's own output
+        assert abs(res[key]["rel_rmse%"] - want) <= 1e-4 * want, key
+        assert res[key]["ms"] > 0
+    assert res["amo_max"]["N"] == 64 and res["amo_fast"]["lo"] == 0.95
+    assert tc.auto_select_mode(x.to(dev), target_rmse=100.0) == "fast"
+    assert tc.auto_select_mode(x.to(dev), target_rmse=0.0) == "G16_max"
+    assert tc.auto_select_mode(x.to(dev), target_rmse=0.0, group_size=16, include_quality=True) == "quality"
