@@ -217,7 +217,7 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
             bool doubtful = false;
 #pragma unroll
             for (int k = 0; k < VPL; ++k) {
-                const float t = __fadd_rn(__fmul_rn(v[k], rcp), zp);
+                const float t = __fmaf_rn(v[k], rcp, zp);  // one rounding fewer than the bound in quant_index assumes
                 kq[k] = rintf(t);
                 doubtful |= !(fabsf(__fsub_rn(t, kq[k])) <= kBoundaryGuard);
             }
