@@ -556,7 +556,7 @@ def main():
         pcie["ceiling_samples_per_s"] = pcie["pinned_h2d_gbs_sum"] * 1e9 / 374640.0
         # the timed region ends when the slowest rank has finished its batches (max over ranks), so with unequal
         # link shares the ceiling of `e2e` is N times the slowest rank's rate, not the sum
-        pcie["ceiling_samples_per_s_max_over_ranks"] = n_gpus * pcie["pinned_h2d_gbs_per_gpu_min"] * 1e9 / 374640.0
+        pcie["ceiling_samples_per_s_max_over_ranks"] = world * pcie["pinned_h2d_gbs_per_gpu_min"] * 1e9 / 374640.0
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
