@@ -160,8 +160,9 @@ TCB_API int tcb_decompress_sym(const int8_t* q, const uint16_t* scales, uint16_t
  *   quant_is_rhs != 0:  out = dense . deq(q)^T   (quantised weight; bias has R_q entries)
  *   quant_is_rhs == 0:  out[R_q, R_d] = deq(q) . dense^T  (the reference's layout: quantised
  *                       activation, dense weight; bias has R_d entries)
- * Requirements: K a positive multiple of 64, G in {16, 32, 64}; dense and q
- * 16-byte aligned.  R_d and R_q are arbitrary (edge tiles are masked).
+ * Requirements: G in {16, 32, 64}, K a positive multiple of G (the kernel steps K by
+ * 64 and zero-fills a ragged last step); dense and q 16-byte aligned.  R_d and R_q
+ * are arbitrary (edge tiles are masked).
  * Every wait inside the kernel is bounded; if one runs out the kernel records it
  * in a per-device status word that tcb_fused_dequant_linear_check() reads.
  */

@@ -334,7 +334,8 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int num_kb = int(p.K / kBlockK);
+    const int num_kb = int((p.K + kBlockK - 1) / kBlockK);  // a ragged last K block is zero-filled by the TMA (dense tile and
+                                                            // codes) and gets zero scales from the chunk fetch
     const int num_tiles = p.tiles_q * p.tiles_d;
 
     if (warp == 0) {
@@ -574,7 +575,8 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     if (R_d < 0 || R_q < 0 || K < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: negative size", who);
     if (!tcb::core_group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
     if (R_d == 0 || R_q == 0) return TCB_OK;
-    if (K == 0 || K % kBlockK != 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: K = %lld must be a positive multiple of %d", who, (long long)K, kBlockK);
+    if (K <= 0 || K % group_size != 0)
+        return tcb::fail(TCB_ERR_BAD_ARG, "%s: K = %lld must be a positive multiple of the group size %d", who, (long long)K, group_size);
     if (!dense || !q || !scales || !out) return tcb::fail(TCB_ERR_BAD_ARG, "%s: null pointer", who);
     if ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(q)) & 15)
         return tcb::fail(TCB_ERR_ALIGNMENT, "%s: dense and q must be 16-byte aligned", who);

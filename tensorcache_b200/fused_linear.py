@@ -10,7 +10,7 @@ along the last dimension) and a dense bf16 ``weight``.  On top of that:
   ``x @ dequant(W).T`` used when the weight matrix is what sits in the cache.
 
 Both run the same kernel; the second writes its output transposed.  The inner
-dimension must be a multiple of 64.
+dimension must be a multiple of the group size.
 """
 from __future__ import annotations
 
@@ -41,8 +41,8 @@ def _launch(dense, q, scales, zp, bias, out, R_d, R_q, K, group_size, quant_is_r
 def _check_common(codes, scales, zp, K, rows, group_size):
     if group_size not in SUPPORTED_GROUP_SIZES:
         raise ValueError(f"group_size {group_size} is not supported, choose from {SUPPORTED_GROUP_SIZES}")
-    if K % 64 != 0:
-        raise ValueError(f"the inner dimension ({K}) must be a multiple of 64 for the fused kernel")
+    if K <= 0 or K % group_size != 0:
+        raise ValueError(f"the inner dimension ({K}) must be a positive multiple of the group size {group_size}")
     groups = rows * K // group_size
     if scales.numel() != groups or scales.dtype != torch.bfloat16:
         raise ValueError(f"expected {groups} bf16 scales, got {scales.numel()} of {scales.dtype}")

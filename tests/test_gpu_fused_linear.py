@@ -31,7 +31,9 @@ def rel_fro(got, ref):
 
 
 @pytest.mark.parametrize("M,N,K,G", [(256, 128, 64, 32), (128, 512, 768, 32), (300, 200, 256, 16), (77, 1000, 1024, 64),
-                                     (1, 1, 64, 32), (2048, 1536, 2048, 32)])
+                                     (1, 1, 64, 32), (2048, 1536, 2048, 32),
+                                     # inner dimensions that are not a multiple of the kernel's K step of 64
+                                     (200, 300, 96, 32), (130, 70, 80, 16), (256, 384, 4000, 32), (64, 64, 192, 64), (33, 77, 16, 16)])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_quantised_weight_matmul(M, N, K, G, with_bias):
     g = torch.Generator().manual_seed(M + N + K)
@@ -100,8 +102,8 @@ def test_dequantised_operand_equals_the_decode_kernel_bits():
 def test_argument_errors():
     x = torch.zeros(8, 96, dtype=torch.bfloat16, device=DEV)
     wq = torch.zeros(8, 96, dtype=torch.uint8, device=DEV)
-    with pytest.raises(ValueError, match="multiple of 64"):
-        tc.fused_dequant_matmul(x, wq, torch.zeros(24, dtype=torch.bfloat16, device=DEV), torch.zeros(24, dtype=torch.uint8, device=DEV))
+    with pytest.raises(ValueError, match="multiple of the group size"):
+        tc.fused_dequant_matmul(x, wq, torch.zeros(12, dtype=torch.bfloat16, device=DEV), torch.zeros(12, dtype=torch.uint8, device=DEV), None, 64)
     wq = torch.zeros(8, 128, dtype=torch.uint8, device=DEV)
     with pytest.raises(ValueError):
         tc.fused_dequant_matmul(torch.zeros(8, 128, dtype=torch.bfloat16, device=DEV), wq,
