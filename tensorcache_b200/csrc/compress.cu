@@ -368,6 +368,222 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
     }
 }
 
+// ------------------------------------------------- one lane per group (G <= 32)
+//
+// For group sizes up to 32 a whole group fits in one thread's registers.  Then nothing is exchanged
+// between lanes: no shuffles, the per-candidate set-up (scale, zero point, reciprocal) is paid once
+// per G values instead of once per G / 4, and the error sum follows the reference's order with plain
+// additions (for G <= 32 every one of ATen's eight lanes adds its values in index order, and the lane
+// totals are added left to right).  x / s is the exact IEEE quotient from the candidate's reciprocal
+// and two FMAs (exact_quotient); the two cases that construction excludes -- a significand of all
+// ones, and quotients so large that the intermediate product could overflow -- take the division.
+
+template <int G, typename T>
+__device__ __forceinline__ void load_group(const T* __restrict__ x, int64_t numel, int64_t base, bool aligned16, float (&v)[G],
+                                           uint32_t& finmask) {
+    constexpr int PER16 = 16 / int(sizeof(T));  // values per 16-byte load
+    if (base + G <= numel && aligned16) {
+        const uint4* p = reinterpret_cast<const uint4*>(x + base);
+#pragma unroll
+        for (int k = 0; k < G / PER16; ++k) {
+            const uint4 w = __ldg(p + k);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (sizeof(T) == 4) {
+                    v[k * 4 + i] = __uint_as_float(ww[i]);
+                } else {
+                    uint16_t lo = uint16_t(ww[i] & 0xffffu), hi = uint16_t(ww[i] >> 16);
+                    v[k * 8 + 2 * i] = widen<T>(*reinterpret_cast<T*>(&lo));
+                    v[k * 8 + 2 * i + 1] = widen<T>(*reinterpret_cast<T*>(&hi));
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < G; ++k) v[k] = base + k < numel ? widen<T>(x[base + k]) : 0.0f;
+    }
+    finmask = 0;
+#pragma unroll
+    for (int k = 0; k < G; ++k) {
+        const bool f = finite_f32(v[k]);
+        if (!f) v[k] = 0.0f;
+        finmask |= (f ? 1u : 0u) << k;
+    }
+}
+
+template <int G>
+__device__ __forceinline__ void store_group(uint8_t* __restrict__ q, int64_t numel, int64_t base, bool aligned8, const uint32_t (&cw)[G / 4]) {
+    if (base + G <= numel && aligned8) {
+#pragma unroll
+        for (int k = 0; k < G / 8; ++k) *reinterpret_cast<uint2*>(q + base + 8 * k) = make_uint2(cw[2 * k], cw[2 * k + 1]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < G; ++k)
+            if (base + k < numel) q[base + k] = uint8_t(cw[k >> 2] >> (8 * (k & 3)));
+    }
+}
+
+// Adds e (the error term of value k) to the reference's running sums: lanes[k % 8] in index order.
+template <int G>
+struct LaneSums {
+    float lanes[8];
+    __device__ __forceinline__ void add(int k, float e) { lanes[k & 7] = k < 8 ? e : __fadd_rn(lanes[k & 7], e); }
+    __device__ __forceinline__ float total() const {
+        float t = lanes[0];
+#pragma unroll
+        for (int l = 1; l < 8; ++l) t = __fadd_rn(t, lanes[l]);
+        return t;
+    }
+};
+
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                            uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
+    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+        const int64_t base = g * G;
+        float v[G];
+        uint32_t finmask;
+        load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
+        float bmin = v[0], bmax = v[0];
+#pragma unroll
+        for (int k = 1; k < G; ++k) {
+            bmin = fminf(bmin, v[k]);
+            bmax = fmaxf(bmax, v[k]);
+        }
+        float rng = fmaxf(__fsub_rn(bmax, bmin), 1e-8f);
+        if (!finite_f32(rng)) rng = 1e-8f;
+        float s0 = __fdiv_rn(rng, 255.0f);
+        if (!finite_f32(s0)) s0 = float(1e-8 / 255.0);
+        const float nbmin = -bmin;
+        const float amax = fmaxf(fabsf(bmin), fabsf(bmax));
+
+        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
+        for (int c = 0; c < tab.n; ++c) {
+            const float s = __fmul_rn(s0, tab.m[c]);
+            const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
+            const float rcp = __frcp_rn(s);
+            LaneSums<G> sums;
+            const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu && __fmul_rn(amax, rcp) < 1048576.0f &&
+                               finmask == kAllFinite;
+            if (plain) {
+#pragma unroll
+                for (int k = 0; k < G; ++k) {
+                    const float qc = clamp255(rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
+                    const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
+                    sums.add(k, __fmul_rn(d, d));
+                }
+            } else {  // rare: divide, and leave out the positions that held NaN / Inf
+#pragma unroll
+                for (int k = 0; k < G; ++k) {
+                    const float qc = clamp255(rintf(__fadd_rn(__fdiv_rn(v[k], s), zp)));
+                    const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
+                    sums.add(k, ((finmask >> k) & 1u) ? __fmul_rn(d, d) : 0.0f);
+                }
+            }
+            const float err = sums.total();
+            if (c == 0 || err < best_err) {
+                best_err = err;
+                best_s = s;
+                best_zp = zp;
+            }
+        }
+
+        uint32_t cw[G / 4];
+        const uint32_t zp8 = uint32_t(best_zp);
+#pragma unroll
+        for (int k = 0; k < G / 4; ++k) cw[k] = 0;
+#pragma unroll
+        for (int k = 0; k < G; ++k) {
+            const float qf = clamp255(rintf(__fadd_rn(__fdiv_rn(v[k], best_s), best_zp)));
+            const uint32_t code = ((finmask >> k) & 1u) ? uint32_t(qf) : zp8;
+            cw[k >> 2] |= code << (8 * (k & 3));
+        }
+        store_group<G>(q, numel, base, out_aligned8, cw);
+        scales[g] = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
+        zps[g] = uint8_t(zp8);
+    }
+}
+
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, uint8_t* __restrict__ q,
+                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
+    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+        const int64_t base = g * G;
+        float v[G];
+        uint32_t finmask;
+        load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
+        float lower = v[0], upper = v[0];
+#pragma unroll
+        for (int k = 1; k < G; ++k) {
+            lower = fminf(lower, v[k]);
+            upper = fmaxf(upper, v[k]);
+        }
+        lower = fminf(lower, 0.0f);
+        upper = fmaxf(upper, 0.0f);
+        const float scale0 = fmaxf(__fsub_rn(__fdiv_rn(upper, 255.0f), __fdiv_rn(lower, 255.0f)), float(1e-8 / 255.0));
+        const int lo_bits = int(__bfloat16_as_short(__float2bfloat16_rn(__fmul_rn(scale0, 0.85f))));
+        const int hi_bits = int(__bfloat16_as_short(__float2bfloat16_rn(__fmul_rn(scale0, 1.10f))));
+        const float nlower = -lower;
+
+        // The range contains zero, so |x| <= upper - lower and |x / s| < 255 / 0.85 + 1 for every candidate: the exact
+        // quotient's intermediate product cannot overflow, and a bf16 scale never has a significand of all ones.
+        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
+        for (int c = 0; c < 64; ++c) {
+            const int bits = lo_bits + c;
+            if (c > 0 && bits > hi_bits) break;
+            const int use = bits < hi_bits ? bits : hi_bits;
+            const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
+            const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
+            const float rcp = __frcp_rn(s);
+            LaneSums<G> sums;
+            if (finmask == kAllFinite) {
+#pragma unroll
+                for (int k = 0; k < G; ++k) {
+                    float e;
+                    (void)quality_code(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)), e);
+                    sums.add(k, e);
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < G; ++k) {
+                    float e;
+                    (void)quality_code(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)), e);
+                    sums.add(k, ((finmask >> k) & 1u) ? e : 0.0f);
+                }
+            }
+            const float tot = sums.total();
+            if (c == 0 || tot < best_err) {
+                best_err = tot;
+                best_s = s;
+                best_zp = zp;
+            }
+        }
+
+        uint32_t cw[G / 4];
+        const uint32_t zp8 = uint32_t(best_zp);
+        const float best_rcp = __frcp_rn(best_s);
+#pragma unroll
+        for (int k = 0; k < G / 4; ++k) cw[k] = 0;
+#pragma unroll
+        for (int k = 0; k < G; ++k) {
+            float e;
+            const float qf = quality_code(v[k], best_s, best_zp, rintf(__fadd_rn(exact_quotient(v[k], best_s, best_rcp), best_zp)), e);
+            const uint32_t code = ((finmask >> k) & 1u) ? uint32_t(qf) : zp8;
+            cw[k >> 2] |= code << (8 * (k & 3));
+        }
+        store_group<G>(q, numel, base, out_aligned8, cw);
+        scales[g] = uint16_t(__float_as_uint(best_s) >> 16);
+        zps[g] = uint8_t(zp8);
+    }
+}
+
 // ------------------------------------------------------------ symmetric codec
 
 __device__ __forceinline__ float clamp_i8(float v) { return fminf(fmaxf(v, -128.0f), 127.0f); }
@@ -643,10 +859,26 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
     const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
     switch (coder) {
     case Coder::Legacy:
-        compress_legacy_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in_aligned, out_aligned);
+        if constexpr (G <= 32) {
+            const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
+            const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
+            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
+            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
+            compress_legacy_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in16, out8);
+        } else {
+            compress_legacy_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in_aligned, out_aligned);
+        }
         break;
     case Coder::Quality:
-        compress_quality_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in_aligned, out_aligned);
+        if constexpr (G <= 32) {
+            const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
+            const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
+            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
+            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
+            compress_quality_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in16, out8);
+        } else {
+            compress_quality_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in_aligned, out_aligned);
+        }
         break;
     default:
         compress_sym_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in_aligned, out_aligned);
