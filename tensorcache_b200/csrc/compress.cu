@@ -652,6 +652,63 @@ compress_sym_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, Can
     }
 }
 
+// The adaptive search of the symmetric codec with one group per lane (G <= 32), like the AMO-BQ lane kernels.
+// |x| <= max|x| and every candidate scale is at least 0.9 max|x| / 127, so the quotients stay below 142.
+template <int G, typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                         uint16_t* __restrict__ scales, bool in_aligned16, bool out_aligned8) {
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
+    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+        const int64_t base = g * G;
+        float v[G];
+        uint32_t finmask;
+        load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
+        float amax = fabsf(v[0]);
+#pragma unroll
+        for (int k = 1; k < G; ++k) amax = fmaxf(amax, fabsf(v[k]));
+        const float s0 = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        float best_s = s0;
+        if (tab.n > 0) {
+            best_s = __fmul_rn(s0, tab.m[0]);  // a group that held NaN / Inf scores NaN / Inf everywhere: candidate 0
+            if (finmask == kAllFinite) {
+                float best_err = 0.0f;
+                for (int c = 0; c < tab.n; ++c) {
+                    const float s = __fmul_rn(s0, tab.m[c]);
+                    const float rcp = __frcp_rn(s);
+                    const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu;
+                    LaneSums<G> sums;
+#pragma unroll
+                    for (int k = 0; k < G; ++k) {
+                        const float quot = plain ? exact_quotient(v[k], s, rcp) : __fdiv_rn(v[k], s);
+                        const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(quot)), s));
+                        sums.add(k, __fmul_rn(d, d));
+                    }
+                    const float err = sums.total();
+                    if (c == 0 || err < best_err) {
+                        best_err = err;
+                        best_s = s;
+                    }
+                }
+            }
+        }
+        const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
+        const float sf = __uint_as_float(uint32_t(sbits) << 16);
+        uint32_t cw[G / 4];
+#pragma unroll
+        for (int k = 0; k < G / 4; ++k) cw[k] = 0;
+#pragma unroll
+        for (int k = 0; k < G; ++k) {
+            const float qf = clamp_i8(rintf(__fdiv_rn(v[k], sf)));
+            const uint32_t code = ((finmask >> k) & 1u) ? (uint32_t(int(qf)) & 0xffu) : 0u;
+            cw[k >> 2] |= code << (8 * (k & 3));
+        }
+        store_group<G>(q, numel, base, out_aligned8, cw);
+        scales[g] = sbits;
+    }
+}
+
 // Plain symmetric codec (no scale search) as a streaming kernel.  One pass over the data, so it is
 // bound by HBM (2 bytes read, 1 + 2/G written per bf16 value), not by arithmetic, and is laid out
 // like the decoder: every thread owns 16 consecutive values (one 256-bit load for 16-bit inputs, two
@@ -881,7 +938,15 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
         }
         break;
     default:
-        compress_sym_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in_aligned, out_aligned);
+        if constexpr (G <= 32) {
+            const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
+            const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
+            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
+            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
+            compress_sym_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in16, out8);
+        } else {
+            compress_sym_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in_aligned, out_aligned);
+        }
         break;
     }
     return cudaGetLastError();
