@@ -251,3 +251,37 @@ def test_benchmark_tensor_and_auto_select_mode(dev, golden_small, golden_extra):
     assert tc.auto_select_mode(x.to(dev), target_rmse=100.0) == "fast"
     assert tc.auto_select_mode(x.to(dev), target_rmse=0.0) == "G16_max"
     assert tc.auto_select_mode(x.to(dev), target_rmse=0.0, group_size=16, include_quality=True) == "quality"
+
+
+def test_encoders_with_unaligned_output_pointers(L, dev):
+    """Codes written to a byte pointer that is not 8-byte aligned (the lane kernels' byte-wise store path)."""
+    from oracle import amo_oracle as orc
+
+    x = bits(synth.config0_style(51, (2, 48, 96)).reshape(-1))
+    n = x.size
+    xd = torch.from_numpy(x.view(np.int16)).to(dev)
+    for G in (8, 16, 24, 32, 64):
+        ng = n // G
+        for mode in ("balanced", "quality", "adaptive"):
+            q = torch.full((n + 16,), 0x5A, dtype=torch.uint8, device=dev)
+            s = torch.zeros(ng, dtype=torch.int16, device=dev)
+            zp = torch.zeros(ng, dtype=torch.uint8, device=dev)
+            off = 3
+            if mode == "adaptive":
+                m = orc.linspace_multipliers(0.90, 1.05, 31)
+                rc = L.tcb_compress_sym(xd.data_ptr(), 0, n, G, m.ctypes.data, 31, q.data_ptr() + off, s.data_ptr(), _stream(dev))
+                want_q, want_s = orc.compress_sym(x, G, True, nthreads=4)
+                want_q = want_q.view(np.uint8)
+            elif mode == "quality":
+                rc = L.tcb_compress_amo_quality(xd.data_ptr(), 0, n, G, q.data_ptr() + off, s.data_ptr(), zp.data_ptr(), _stream(dev))
+                want_q, want_s, _ = orc.compress(x, G, "quality", nthreads=4)
+            else:
+                m = orc.linspace_multipliers(0.95, 1.05, 32)
+                rc = L.tcb_compress_amo(xd.data_ptr(), 0, n, G, m.ctypes.data, 32, q.data_ptr() + off, s.data_ptr(), zp.data_ptr(), _stream(dev))
+                want_q, want_s, _ = orc.compress(x, G, "balanced", nthreads=4)
+            assert rc == 0, L.tcb_last_error()
+            torch.cuda.synchronize(dev)
+            qh = q.cpu().numpy()
+            assert np.all(qh[:off] == 0x5A) and np.all(qh[off + n:] == 0x5A), (G, mode, "wrote outside")
+            assert np.array_equal(qh[off:off + n], want_q), (G, mode)
+            assert np.array_equal(s.cpu().numpy().view(np.uint16), want_s), (G, mode)
