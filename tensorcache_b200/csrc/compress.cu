@@ -378,9 +378,15 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
 // and two FMAs (exact_quotient); the two cases that construction excludes -- a significand of all
 // ones, and quotients so large that the intermediate product could overflow -- take the division.
 
+template <int G>
+struct GroupMask {
+    using type = uint64_t;  // one bit per value of the group
+    static constexpr type kAll = G >= 64 ? ~uint64_t(0) : (uint64_t(1) << (G & 63)) - 1;
+};
+
 template <int G, typename T>
 __device__ __forceinline__ void load_group(const T* __restrict__ x, int64_t numel, int64_t base, bool aligned16, float (&v)[G],
-                                           uint32_t& finmask) {
+                                           uint64_t& finmask) {
     constexpr int PER16 = 16 / int(sizeof(T));  // values per 16-byte load
     if (base + G <= numel && aligned16) {
         const uint4* p = reinterpret_cast<const uint4*>(x + base);
@@ -408,7 +414,7 @@ __device__ __forceinline__ void load_group(const T* __restrict__ x, int64_t nume
     for (int k = 0; k < G; ++k) {
         const bool f = finite_f32(v[k]);
         if (!f) v[k] = 0.0f;
-        finmask |= (f ? 1u : 0u) << k;
+        finmask |= uint64_t(f ? 1 : 0) << k;
     }
 }
 
@@ -424,15 +430,32 @@ __device__ __forceinline__ void store_group(uint8_t* __restrict__ q, int64_t num
     }
 }
 
-// Adds e (the error term of value k) to the reference's running sums: lanes[k % 8] in index order.
+// The reference's running sums for the error terms of one group, fed in index order.  ATen keeps eight lanes
+// (value k belongs to lane k % 8); within a lane complete runs of four 8-wide vectors go to four accumulators
+// (vector v to accumulator v % 4), left-over vectors to accumulator 0, the accumulators are combined
+// ((a0 + a1) + a2) + a3 and the lane totals added left to right.  For G <= 32 that is one accumulator per lane
+// in index order; G = 64 needs all four.
 template <int G>
 struct LaneSums {
-    float lanes[8];
-    __device__ __forceinline__ void add(int k, float e) { lanes[k & 7] = k < 8 ? e : __fadd_rn(lanes[k & 7], e); }
+    static constexpr int NVEC = G / 8, FULL = (NVEC / 4) * 4, NACC = (FULL > 4 || (FULL == 4 && NVEC > 4)) ? 4 : 1;
+    float acc[NACC][8];
+    __device__ __forceinline__ void add(int k, float e) {
+        const int vI = k >> 3, l = k & 7;
+        if (NACC == 1) {
+            acc[0][l] = vI == 0 ? e : __fadd_rn(acc[0][l], e);
+        } else {
+            const int t = vI < FULL ? (vI & 3) : 0;
+            const bool first = vI < 4;
+            acc[t][l] = first ? e : __fadd_rn(acc[t][l], e);
+        }
+    }
     __device__ __forceinline__ float total() const {
-        float t = lanes[0];
+        float t = 0.0f;
 #pragma unroll
-        for (int l = 1; l < 8; ++l) t = __fadd_rn(t, lanes[l]);
+        for (int l = 0; l < 8; ++l) {
+            const float lt = NACC == 1 ? acc[0][l] : __fadd_rn(__fadd_rn(__fadd_rn(acc[0][l], acc[1][l]), acc[2][l]), acc[3][l]);
+            t = l == 0 ? lt : __fadd_rn(t, lt);
+        }
         return t;
     }
 };
@@ -441,12 +464,12 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
-    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
         float v[G];
-        uint32_t finmask;
+        uint64_t finmask;
         load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
         float bmin = v[0], bmax = v[0];
 #pragma unroll
@@ -512,12 +535,12 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, uint8_t* __restrict__ q,
                              uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
-    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
         float v[G];
-        uint32_t finmask;
+        uint64_t finmask;
         load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
         float lower = v[0], upper = v[0];
 #pragma unroll
@@ -658,12 +681,12 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                          uint16_t* __restrict__ scales, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32, "one group per lane needs G <= 32");
-    constexpr uint32_t kAllFinite = G == 32 ? 0xffffffffu : (1u << (G & 31)) - 1u;
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
         float v[G];
-        uint32_t finmask;
+        uint64_t finmask;
         load_group<G, T>(x, numel, base, in_aligned16, v, finmask);
         float amax = fabsf(v[0]);
 #pragma unroll
@@ -679,11 +702,18 @@ compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups
                     const float rcp = __frcp_rn(s);
                     const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu;
                     LaneSums<G> sums;
+                    if (plain) {
 #pragma unroll
-                    for (int k = 0; k < G; ++k) {
-                        const float quot = plain ? exact_quotient(v[k], s, rcp) : __fdiv_rn(v[k], s);
-                        const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(quot)), s));
-                        sums.add(k, __fmul_rn(d, d));
+                        for (int k = 0; k < G; ++k) {
+                            const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(exact_quotient(v[k], s, rcp))), s));
+                            sums.add(k, __fmul_rn(d, d));
+                        }
+                    } else {  // rare: a scale whose significand is all ones takes the division
+#pragma unroll
+                        for (int k = 0; k < G; ++k) {
+                            const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(__fdiv_rn(v[k], s))), s));
+                            sums.add(k, __fmul_rn(d, d));
+                        }
                     }
                     const float err = sums.total();
                     if (c == 0 || err < best_err) {
@@ -916,7 +946,7 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
     const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
     switch (coder) {
     case Coder::Legacy:
-        if constexpr (G <= 32) {
+        if constexpr (G <= 32 || G == 64) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
             const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
