@@ -264,6 +264,16 @@ compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, 
 
 // ------------------------------------------------------------------ quality mode
 
+// The smallest decoded squared error over the codes r - 1, r, r + 1 (each clamped): what the candidate search of the
+// quality mode scores.  The values are finite here (NaN / Inf were cleaned), so a plain minimum equals the reference's
+// NaN-propagating one.
+__device__ __forceinline__ float quality_error(float x, float s, float zp, float r) {
+    const float d0 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(r), zp), s)));
+    const float d1 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r, -1.0f)), zp), s)));
+    const float d2 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r, 1.0f)), zp), s)));
+    return fminf(fminf(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2));
+}
+
 // code choice of the reference's _amo_quality_codes for one value whose rounded index r = rint(x / s + zp)
 // is already known: r, r - 1 and r + 1 are tried in that order and the first smallest decoded error wins
 __device__ __forceinline__ float quality_code(float x, float s, float zp, float r, float& err_out) {
@@ -337,7 +347,7 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             float e[VPL];
 #pragma unroll
             for (int i = 0; i < VPL; ++i)
-                (void)quality_code(v[i], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)), e[i]);
+                e[i] = quality_error(v[i], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)));
             if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
                 for (int i = 0; i < VPL; ++i)
@@ -569,15 +579,12 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
             if (finmask == kAllFinite) {
 #pragma unroll
                 for (int k = 0; k < G; ++k) {
-                    float e;
-                    (void)quality_code(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)), e);
-                    sums.add(k, e);
+                    sums.add(k, quality_error(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp))));
                 }
             } else {
 #pragma unroll
                 for (int k = 0; k < G; ++k) {
-                    float e;
-                    (void)quality_code(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)), e);
+                    const float e = quality_error(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
                     sums.add(k, ((finmask >> k) & 1u) ? e : 0.0f);
                 }
             }
