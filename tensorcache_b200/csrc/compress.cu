@@ -474,7 +474,7 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
@@ -545,7 +545,7 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, uint8_t* __restrict__ q,
                              uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
@@ -688,7 +688,7 @@ template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                          uint16_t* __restrict__ scales, bool in_aligned16, bool out_aligned8) {
-    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 64, "group sizes with a one-group-per-lane kernel");
+    static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
     for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
         const int64_t base = g * G;
@@ -953,7 +953,7 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
     const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
     switch (coder) {
     case Coder::Legacy:
-        if constexpr (G <= 32 || G == 64) {
+        if constexpr (G <= 64) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
             const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
