@@ -975,7 +975,7 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
         }
         break;
     default:
-        if constexpr (G <= 32) {
+        if constexpr (G <= 64) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
             const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
