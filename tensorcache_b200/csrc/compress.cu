@@ -274,6 +274,27 @@ __device__ __forceinline__ float quality_error(float x, float s, float zp, float
     return fminf(fminf(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2));
 }
 
+// quality_error for two values at once: the six bf16 roundings become three packed conversions (the capture of
+// the one-value form showed the conversion pipe, not the issue slots, closest to its limit).
+__device__ __forceinline__ void round_bf16_pair(float a, float b, float& ra, float& rb) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);  // .x = a (low half)
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&p);
+    ra = __uint_as_float(w << 16);
+    rb = __uint_as_float(w & 0xffff0000u);
+}
+__device__ __forceinline__ void quality_error2(float x0, float x1, float s, float zp, float r0, float r1, float& e0, float& e1) {
+    float a0, a1, b0, b1, c0, c1;
+    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(r0), zp), s), __fmul_rn(__fsub_rn(clamp255(r1), zp), s), a0, a1);
+    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r0, -1.0f)), zp), s),
+                    __fmul_rn(__fsub_rn(clamp255(__fadd_rn(r1, -1.0f)), zp), s), b0, b1);
+    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r0, 1.0f)), zp), s),
+                    __fmul_rn(__fsub_rn(clamp255(__fadd_rn(r1, 1.0f)), zp), s), c0, c1);
+    const float da0 = __fsub_rn(x0, a0), db0 = __fsub_rn(x0, b0), dc0 = __fsub_rn(x0, c0);
+    const float da1 = __fsub_rn(x1, a1), db1 = __fsub_rn(x1, b1), dc1 = __fsub_rn(x1, c1);
+    e0 = fminf(fminf(__fmul_rn(da0, da0), __fmul_rn(db0, db0)), __fmul_rn(dc0, dc0));
+    e1 = fminf(fminf(__fmul_rn(da1, da1), __fmul_rn(db1, db1)), __fmul_rn(dc1, dc1));
+}
+
 // code choice of the reference's _amo_quality_codes for one value whose rounded index r = rint(x / s + zp)
 // is already known: r, r - 1 and r + 1 are tried in that order and the first smallest decoded error wins
 __device__ __forceinline__ float quality_code(float x, float s, float zp, float r, float& err_out) {
@@ -346,8 +367,9 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             // rounded index from the exact quotient (the scale is a bf16 value), then the three-way code choice
             float e[VPL];
 #pragma unroll
-            for (int i = 0; i < VPL; ++i)
-                e[i] = quality_error(v[i], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)));
+            for (int i = 0; i < VPL; i += 2)
+                quality_error2(v[i], v[i + 1], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)),
+                               rintf(__fadd_rn(exact_quotient(v[i + 1], s, rcp), zp)), e[i], e[i + 1]);
             if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
                 for (int i = 0; i < VPL; ++i)
@@ -578,8 +600,12 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
             LaneSums<G> sums;
             if (finmask == kAllFinite) {
 #pragma unroll
-                for (int k = 0; k < G; ++k) {
-                    sums.add(k, quality_error(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp))));
+                for (int k = 0; k < G; k += 2) {
+                    float e0, e1;
+                    quality_error2(v[k], v[k + 1], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)),
+                                   rintf(__fadd_rn(exact_quotient(v[k + 1], s, rcp), zp)), e0, e1);
+                    sums.add(k, e0);
+                    sums.add(k + 1, e1);
                 }
             } else {
 #pragma unroll
