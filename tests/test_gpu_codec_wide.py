@@ -285,3 +285,34 @@ def test_encoders_with_unaligned_output_pointers(L, dev):
             assert np.all(qh[:off] == 0x5A) and np.all(qh[off + n:] == 0x5A), (G, mode, "wrote outside")
             assert np.array_equal(qh[off:off + n], want_q), (G, mode)
             assert np.array_equal(s.cpu().numpy().view(np.uint16), want_s), (G, mode)
+
+
+def test_more_than_two_to_the_31_values(dev):
+    """Index arithmetic past 2^31: encode (fast preset and plain symmetric) and decode 2^31 + 4096 + 5 values,
+    checked against the oracle on windows at the start, across the 2^31 boundary and at the ragged end."""
+    import tensorcache_b200 as tc
+    from oracle import amo_oracle as orc
+
+    n = (1 << 31) + 4096 + 5
+    G = 32
+    gen = torch.Generator(device=dev).manual_seed(99)
+    tile = (torch.randn(1 << 20, generator=gen, device=dev) * 3).to(torch.bfloat16)
+    x = tile.repeat((n + tile.numel() - 1) // tile.numel())[:n].contiguous()
+    x[(1 << 31) - 7:(1 << 31) + 9] = torch.arange(16, device=dev, dtype=torch.float32).to(torch.bfloat16) - 4   # distinct values at the boundary
+    windows = [(0, 1 << 16), ((1 << 31) - (1 << 15), (1 << 31) + (1 << 15)), (n - (1 << 15) - 5, n)]
+    windows = [(a // G * G, b) for a, b in windows]
+    q, s, zp, _ = tc.compress(x, "fast", G)
+    rec = tc.decompress(q, s, (n,), zp, G)
+    sq, ss, _ = tc.compress(x, "sym", G)
+    srec = tc.decompress(sq, ss, (n,), None, G)
+    torch.cuda.synchronize(dev)
+    for a, b in windows:
+        xw = bits(x[a:b].cpu())
+        oq, os_, ozp = orc.compress(xw, G, "fast", nthreads=4)
+        ga, gb = a // G, (b + G - 1) // G
+        assert np.array_equal(q[a:b].cpu().numpy(), oq), (a, b)
+        assert np.array_equal(bits(s[ga:gb].cpu()), os_) and np.array_equal(zp[ga:gb].cpu().numpy(), ozp), (a, b)
+        assert np.array_equal(bits(rec[a:b].cpu()), orc.decompress(oq, os_, ozp, G)), (a, b)
+        osq, oss = orc.compress_sym(xw, G, False, nthreads=4)
+        assert np.array_equal(sq[a:b].cpu().numpy(), osq) and np.array_equal(bits(ss[ga:gb].cpu()), oss), ("sym", a, b)
+        assert np.array_equal(bits(srec[a:b].cpu()), orc.decompress_sym(osq, oss, G)), ("sym", a, b)
