@@ -222,3 +222,27 @@ def test_larger_symmetric_cache_round_trip(tmp_path):
             np.random.seed(8)
             got = bits(torch.cat([b.clone() for b in st])).reshape(300, -1)
             assert np.array_equal(got, want[st.indices])
+
+
+def test_benchmark_shape_cache_round_trip(tmp_path):
+    """The benchmark's sample shape [446, 768], B = 128, two shards of 160 samples: every reader mode returns the
+    bits of decompress(compress(rows)), contiguous and shuffled, with a partial last batch."""
+    x = synth.config0_style(4, (320, 446, 768))
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 320, 446, 768, group_size=32, amo_bq=True, amo_mode="balanced", num_shards=2)
+    w.append(x[:200].to(DEV)); w.append(x[200:]); w.close()
+    q, s, zp, _ = tc.compress(x.to(DEV), "balanced", 32)
+    want = tc.decompress(q, s, (320, 446, 768), zp, 32)
+    for kw in (dict(), dict(pin_shard=True)):
+        with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=128, device=DEV, shuffle=False, **kw) as st:
+            assert len(st) == 3
+            got = torch.cat([b.clone() for b in st])
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16)), kw
+            st.shuffle = True
+            np.random.seed(12)
+            got = torch.cat([b.clone() for b in st])
+            idx = torch.from_numpy(st.indices.copy()).to(DEV)
+            assert torch.equal(got.view(torch.int16), want[idx].view(torch.int16)), kw
+    for r in range(2):
+        with tc.FeatureCacheDataset(tmp_path / "feat", rank=r, world_size=2) as ds:
+            got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=128, shuffle=False, device=DEV)])
+            assert torch.equal(got.view(torch.int16), want[160 * r:160 * (r + 1)].view(torch.int16))
