@@ -42,7 +42,8 @@ enum tcb_status {
     TCB_ERR_TIMEOUT = 4,       /* a bounded device-side wait ran out               */
     TCB_ERR_ALIGNMENT = 5,     /* pointer or extent not aligned as the entry needs */
     TCB_ERR_TOO_LARGE = 6,     /* size beyond what the entry point supports        */
-    TCB_ERR_IO = 7             /* host-side file / mapping problem                 */
+    TCB_ERR_IO = 7,            /* host-side file / mapping problem                 */
+    TCB_ERR_SUM_ORDER = 8      /* tcb_selftest_sum_order: the host adds in another order */
 };
 
 /* element types accepted by the compressor */
@@ -53,6 +54,17 @@ TCB_API int tcb_version(void);
 
 /* Message of the last failure on the calling host thread ("" if none). */
 TCB_API const char* tcb_last_error(void);
+
+/*
+ * Host-only self-test of the one ISA-dependent assumption of the encoders: the order in
+ * which the G squared errors of a group are added (cand_err.sum(dim=-1),
+ * src/tensorcache/codec.py:877; torch's CPU reduction: 8 lanes x 4 accumulators, lane totals
+ * left to right).  `rows` holds n_rows x group_size fp32 terms, `host_sums` the n_rows sums
+ * the host's torch computed for them; the function adds each row in the order the encode
+ * kernels use and compares the bits.  Returns TCB_OK, or TCB_ERR_SUM_ORDER with the first
+ * differing row in tcb_last_error().  Touches no GPU.
+ */
+TCB_API int tcb_selftest_sum_order(const float* rows, int64_t n_rows, int group_size, const float* host_sums);
 
 /*
  * AMO-BQ decode:  out[i] = bf16_rne((f32(q[i]) - f32(zp[i / G])) * f32(scale[i / G])).
@@ -88,8 +100,15 @@ TCB_API int tcb_decompress_amo(const uint8_t* q, const uint16_t* scales, const u
  * TCB_ERR_TOO_LARGE (split the tensor at a multiple of the group size).
  * The call enqueues three host-to-device copies and the decode kernel on `stream`
  * and calls no cudaMalloc / cudaFree or any other allocating routine.  The first
- * call on each device looks up the array's device address (cudaGetSymbolAddress);
- * make that first call outside any stream capture.  All calls on one device share
+ * call on each device is the set-up call: it looks up the array's device address
+ * (cudaGetSymbolAddress) and makes the decode kernels of all three group sizes and
+ * every output alignment resident there.  Under CUDA's lazy module loading that is
+ * the moment the array and the kernel code take their device memory, so make this
+ * first call -- any size, numel = 32 will do -- per device while allocation is still
+ * allowed: before the process freezes its memory plan and outside any stream
+ * capture.  Later calls load nothing.  `stream` must belong to the device that is
+ * current when the call is made (its copy of the array is the one used).
+ * All calls on one device share
  * the one array, which keeps the previous call's bytes: every byte a call reads
  * it has overwritten first, so nothing needs clearing, but two calls whose work
  * overlaps on the GPU (different streams, no ordering between them) race on it.
@@ -193,6 +212,16 @@ TCB_API int tcb_selftest_bounded_wait(int budget_ms, void* stream);
  */
 TCB_API int tcb_gather_rows(void* dst, const void* src_base, int64_t row_bytes, const int64_t* idx,
                     int64_t first_row, int64_t n, int nthreads);
+
+/*
+ * Host-side block copy used by the cache writer: copies `bytes` bytes from `src`
+ * (page-locked landing buffer of a chunk of codes) to `dst`, a range of a writable
+ * mapping of a cache file, on up to nthreads worker threads.  Each worker has the
+ * kernel populate its part of a still sparse file in one call before it copies, so
+ * the copy does not take one page fault per 4 KB.  Replaces the row assignments into
+ * np.memmap of FeatureCacheWriter.append (src/tensorcache/feature_cache.py:364-424).
+ */
+TCB_API int tcb_write_block(void* dst, const void* src, int64_t bytes, int nthreads);
 
 /*
  * Native double-buffered batch pipeline behind ZeroCopyTensorStreamer

@@ -14,13 +14,13 @@ from .codec import (AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, 
 from .feature_cache import FeatureCacheDataset, FeatureCacheWriter
 from .fused_linear import FusedDequantLinear, fused_dequant_matmul
 from .streamer import ZeroCopyTensorStreamer
-from .utils import auto_select_mode, benchmark_tensor, compress, decompress, estimate_compression
+from .utils import auto_select_mode, benchmark_tensor, compress, decompress, estimate_compression, selftest_sum_order
 
 __version__ = "0.1.0"
 __all__ = [
     "AMO_BQ_PRESETS", "BlockwiseInt8Codec", "quantize_int8_amo_bq", "dequantize_int8_amo_bq",
     "quantize_int8_g32", "quantize_int8_adaptive", "dequantize_int8_g32",
-    "compress", "decompress", "estimate_compression", "benchmark_tensor", "auto_select_mode",
+    "compress", "decompress", "estimate_compression", "benchmark_tensor", "auto_select_mode", "selftest_sum_order",
     "FusedDequantLinear", "fused_dequant_matmul",
     "FeatureCacheWriter", "FeatureCacheDataset", "ZeroCopyTensorStreamer",
 ]

@@ -13,7 +13,7 @@ _PKG = Path(__file__).resolve().parent
 LIB_PATH = _PKG / "libtcb200.so"
 
 TCB_OK = 0
-ERR_BAD_ARG, ERR_GROUP_SIZE, ERR_CUDA, ERR_TIMEOUT, ERR_ALIGNMENT, ERR_TOO_LARGE, ERR_IO = 1, 2, 3, 4, 5, 6, 7
+ERR_BAD_ARG, ERR_GROUP_SIZE, ERR_CUDA, ERR_TIMEOUT, ERR_ALIGNMENT, ERR_TOO_LARGE, ERR_IO, ERR_SUM_ORDER = 1, 2, 3, 4, 5, 6, 7, 8
 DT_BF16, DT_F16, DT_F32 = 0, 1, 2
 NOALLOC_MAX_VALUES = 4 * 1024 * 1024  # TCB_NOALLOC_MAX_VALUES
 
@@ -51,6 +51,7 @@ class StreamerDesc(ctypes.Structure):
 SIGNATURES = {
     "tcb_version": (_i32, []),
     "tcb_last_error": (ctypes.c_char_p, []),
+    "tcb_selftest_sum_order": (_i32, [_vp, _i64, _i32, _vp]),
     "tcb_decompress_amo": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_decompress_amo_host_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "tcb_compress_amo": (_i32, [_vp, _i32, _i64, _i32, _vp, _i32, _vp, _vp, _vp, _vp]),
@@ -61,6 +62,7 @@ SIGNATURES = {
     "tcb_fused_dequant_linear_check": (_i32, [_vp]),
     "tcb_selftest_bounded_wait": (_i32, [_i32, _vp]),
     "tcb_gather_rows": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64, _i32]),
+    "tcb_write_block": (_i32, [_vp, _vp, _i64, _i32]),
     "tcb_pin_host_range": (_i32, [_vp, _i64]),
     "tcb_unpin_host_range": (_i32, [_vp]),
     "tcb_streamer_create": (_i32, [ctypes.POINTER(StreamerDesc), ctypes.POINTER(_vp)]),

@@ -39,6 +39,8 @@ class CacheLayout:
     total_shards_on_disk: int = 1
     selected: Optional[List[int]] = None   # shard numbers opened, None = unsharded cache
     private: bool = False                   # mapped copy-on-write so that the mappings can be page-locked
+    pinned_ranges: List[int] = field(default_factory=list)   # start addresses of the page-locked mappings
+    pinned_device: Optional[object] = None
 
     @property
     def groups_per_sample(self) -> int:
@@ -71,7 +73,52 @@ class CacheLayout:
                 return si, idx - off
         raise IndexError(idx)
 
+    @property
+    def nbytes(self) -> int:
+        """Bytes of the opened shard files."""
+        return sum(a.nbytes for sh in self.shards if sh.num_samples > 0 for a in (sh.q, sh.s, sh.zp) if a is not None)
+
+    def pin(self, device) -> None:
+        """Page-locks the mapped shard files (once; needs ``private`` mappings) so that the copy engine and the
+        gather kernel read them in place.  Costs the shards' size in host memory and about 0.4 s per GB."""
+        if self.pinned_ranges:
+            return
+        if not self.private:
+            raise ValueError("page-locking needs a cache opened with private=True (copy-on-write mappings)")
+        import torch
+        with torch.cuda.device(device):
+            try:
+                for sh in self.shards:
+                    if sh.num_samples == 0:
+                        continue
+                    for arr in (sh.q, sh.s, sh.zp):
+                        if arr is None:
+                            continue
+                        nbytes = (arr.nbytes + 4095) // 4096 * 4096   # the mapping covers whole pages
+                        _lib.check(_lib.lib().tcb_pin_host_range(ctypes.c_void_p(arr.ctypes.data), nbytes))
+                        self.pinned_ranges.append(arr.ctypes.data)
+            except Exception:
+                self.unpin()
+                raise
+        self.pinned_device = device
+
+    def unpin(self) -> None:
+        if not self.pinned_ranges:
+            return
+        import torch
+        ctx = torch.cuda.device(self.pinned_device) if self.pinned_device is not None and torch.cuda.is_available() else None
+        if ctx is not None:
+            ctx.__enter__()
+        try:
+            for addr in self.pinned_ranges:
+                _lib.lib().tcb_unpin_host_range(ctypes.c_void_p(addr))
+        finally:
+            if ctx is not None:
+                ctx.__exit__(None, None, None)
+        self.pinned_ranges = []
+
     def close(self):
+        self.unpin()
         for sh in self.shards:
             for name in ("q", "s", "zp"):
                 mm = getattr(sh, name)
@@ -189,8 +236,62 @@ def default_gather_threads() -> int:
     return max(1, min(8, n // max(1, local_ranks) - 1))
 
 
+def writer_threads() -> int:
+    """Copy workers of the cache writer: this process's share of the cores, at most 16."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        local_ranks = int(os.environ.get("LOCAL_WORLD_SIZE") or os.environ.get("WORLD_SIZE") or 1)
+    except ValueError:
+        local_ranks = 1
+    return max(1, min(16, n // max(1, local_ranks)))
+
+
+MEM_FRACTION_FOR_RESIDENT_SHARDS = 0.25   # automatic mode page-locks shards only up to this share of MemAvailable
+
+
+def _mem_available_bytes() -> Optional[int]:
+    try:
+        with open("/proc/meminfo", "r") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) * 1024
+    except (OSError, ValueError, IndexError):
+        pass
+    return None
+
+
+def try_make_resident(layout: CacheLayout, device: torch.device, wanted: Optional[bool]) -> bool:
+    """Decides the reader mode.  ``wanted`` True: page-lock the opened shards or raise.  False: never.
+    None (automatic): page-lock them when they fit ``MEM_FRACTION_FOR_RESIDENT_SHARDS`` of the host memory that is
+    available right now and the driver agrees; otherwise say why in one warning and let the reader copy
+    rows through page-locked staging as the reference does."""
+    if wanted is False or layout.num_samples == 0:
+        return False
+    if layout.pinned_ranges:
+        return True
+    if wanted:
+        layout.pin(device)
+        return True
+    import warnings
+    avail = _mem_available_bytes()
+    need = layout.nbytes
+    if avail is not None and need > MEM_FRACTION_FOR_RESIDENT_SHARDS * avail:
+        warnings.warn(f"tensorcache_b200: the opened shard(s) hold {need / 2**30:.1f} GiB, more than "
+                      f"{MEM_FRACTION_FOR_RESIDENT_SHARDS:.0%} of the {avail / 2**30:.1f} GiB of host memory available; "
+                      "reading through page-locked staging copies instead of keeping the shard page-locked", stacklevel=3)
+        return False
+    try:
+        layout.pin(device)
+        return True
+    except Exception as e:   # the driver refused (memlock limit, unsupported mapping): the staging mode still works
+        warnings.warn(f"tensorcache_b200: could not page-lock the shard files ({e}); reading through page-locked "
+                      "staging copies instead", stacklevel=3)
+        return False
+
+
 class NativePipeline:
-    """Owns the ring buffers (torch tensors) and the native streamer handle."""
+    """Owns the ring buffers (torch tensors) and the native streamer handle.  With ``pin_shards`` the shard
+    files must already be page-locked (``CacheLayout.pin``); the copies then start from the mappings."""
 
     def __init__(self, layout: CacheLayout, batch_size: int, device: torch.device, n_slots: int,
                  n_threads: Optional[int] = None, pin_shards: bool = False):
@@ -206,34 +307,48 @@ class NativePipeline:
         gps = layout.groups_per_sample
         B = self.batch_size
         self.pin_shards = bool(pin_shards)
-        self._pinned_ranges = []
-        if self.pin_shards:
-            if not layout.private:
-                raise ValueError("pin_shards needs a cache opened with private=True (copy-on-write mappings)")
-            with torch.cuda.device(device):
-                try:
-                    for sh in layout.shards:
-                        if sh.num_samples == 0:
-                            continue
-                        for arr in (sh.q, sh.s, sh.zp):
-                            if arr is None:
-                                continue
-                            nbytes = (arr.nbytes + 4095) // 4096 * 4096   # the mapping covers whole pages
-                            _lib.check(_lib.lib().tcb_pin_host_range(ctypes.c_void_p(arr.ctypes.data), nbytes))
-                            self._pinned_ranges.append(arr.ctypes.data)
-                except Exception:
-                    self._unpin()
-                    raise
-        # the staging copy of the codes is not needed when the copy engine reads the shard itself
+        if self.pin_shards and not layout.pinned_ranges and layout.num_samples > 0:
+            layout.pin(device)
+        # One page-locked block and one device block per ring slot, laid out [codes | scales | zero points], so that a
+        # full batch crosses PCIe as one copy.  The staging copy of the codes is not needed when the copy engine reads
+        # the shard itself.
         amo = layout.amo_bq
         qdt = torch.uint8 if amo else torch.int8
-        self.pinned_q = [] if self.pin_shards else [
-            torch.empty((B, layout.seq_len, layout.dim), dtype=qdt, pin_memory=True) for _ in range(n_slots)]
-        self.pinned_s = [torch.empty((B, gps), dtype=torch.bfloat16, pin_memory=True) for _ in range(n_slots)]
-        self.pinned_zp = [torch.empty((B, gps), dtype=torch.uint8, pin_memory=True) for _ in range(n_slots)] if amo else None
-        self.dev_q = [torch.empty((B, layout.seq_len, layout.dim), dtype=qdt, device=device) for _ in range(n_slots)]
-        self.dev_s = [torch.empty((B, gps), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
-        self.dev_zp = [torch.empty((B, gps), dtype=torch.uint8, device=device) for _ in range(n_slots)] if amo else None
+        qb, sb, zb = B * vps, B * gps * 2, (B * gps if amo else 0)
+        qb_pad, sb_pad = (qb + 255) // 256 * 256, (sb + 255) // 256 * 256
+        contiguous = qb_pad == qb and sb_pad == sb     # otherwise the three arrays keep their own 256-byte alignment
+        self._contiguous_slots = contiguous
+
+        def carve(block, with_q):
+            off = 0
+            q = s = z = None
+            if with_q:
+                q = block[off:off + qb].view(qdt).view(B, layout.seq_len, layout.dim)
+                off += qb_pad
+            s = block[off:off + sb].view(torch.bfloat16).view(B, gps)
+            off += sb_pad
+            if amo:
+                z = block[off:off + zb].view(B, gps)
+            return q, s, z
+
+        self._pinned_blocks, self._dev_blocks = [], []
+        self.pinned_q, self.pinned_s, self.pinned_zp = [], [], ([] if amo else None)
+        self.dev_q, self.dev_s, self.dev_zp = [], [], ([] if amo else None)
+        for _ in range(n_slots):
+            hb = torch.empty((0 if self.pin_shards else qb_pad) + sb_pad + zb, dtype=torch.uint8, pin_memory=True)
+            db = torch.empty(qb_pad + sb_pad + zb, dtype=torch.uint8, device=device)
+            self._pinned_blocks.append(hb)
+            self._dev_blocks.append(db)
+            hq, hs, hz = carve(hb, not self.pin_shards)
+            dq, ds, dz = carve(db, True)
+            if hq is not None:
+                self.pinned_q.append(hq)
+            self.pinned_s.append(hs)
+            self.dev_q.append(dq)
+            self.dev_s.append(ds)
+            if amo:
+                self.pinned_zp.append(hz)
+                self.dev_zp.append(dz)
         self.dev_out = [torch.empty((B, layout.seq_len, layout.dim), dtype=torch.bfloat16, device=device) for _ in range(n_slots)]
 
         def table(tensors):
@@ -293,19 +408,12 @@ class NativePipeline:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().tcb_streamer_release(self._handle, self._stream()))
 
-    def _unpin(self):
-        for addr in self._pinned_ranges:
-            _lib.lib().tcb_unpin_host_range(ctypes.c_void_p(addr))
-        self._pinned_ranges = []
-
     def close(self):
+        """Stops the native pipeline and drops the ring.  The shard files stay page-locked until the layout closes."""
         if getattr(self, "_handle", None) is not None and self._handle.value:
             _lib.lib().tcb_streamer_destroy(self._handle)
             self._handle = ctypes.c_void_p()
-        if getattr(self, "_pinned_ranges", None):
-            with torch.cuda.device(self.device):
-                self._unpin()
-        for name in ("pinned_q", "pinned_s", "pinned_zp", "dev_q", "dev_s", "dev_zp", "dev_out"):
+        for name in ("pinned_q", "pinned_s", "pinned_zp", "dev_q", "dev_s", "dev_zp", "dev_out", "_pinned_blocks", "_dev_blocks"):
             setattr(self, name, None)
 
     def __del__(self):

@@ -1,24 +1,39 @@
 // AMO-BQ encode kernels for sm_100a: per-group asymmetric min/max plus the scale
 // search of the reference's CPU path, reproduced bit for bit.
 //
-// Work split: four lanes ("a quad") per group.  Lane j of the quad owns columns
-// 2j and 2j+1 of every 8-wide vector of the group, i.e. G/4 values in registers.
-// That split is chosen so that the squared-error sum can follow the order of the
-// reference's CPU reduction exactly (8 lanes x 4 partial accumulators per lane,
-// then the 8 lane totals left to right): each GPU lane accumulates its two
-// columns privately in that order and the four lanes chain their totals with
-// warp shuffles.  Min/max use xor-shuffles inside the quad.
+// Two families of kernels share the arithmetic:
+//   * "lane" kernels (compress_legacy_lane_kernel, compress_quality_lane_kernel,
+//     compress_sym_lane_kernel) -- the hot path for G <= 32, and for G = 48 / 64 with
+//     the candidate-table presets: ONE group per lane.  The group's values stay in the
+//     thread's registers, nothing crosses lanes, the per-candidate set-up (scale, zero
+//     point, reciprocal) is paid once per G values, and the squared-error sum follows
+//     the reference's order with plain additions in the right sequence.
+//   * "quad" kernels (compress_legacy_kernel, compress_quality_kernel, compress_sym_kernel)
+//     -- G = 128, and G = 48 / 64 in quality mode, where a group does not fit one thread's
+//     registers: four lanes per group.  Lane j of the quad owns columns 2j and 2j+1 of
+//     every 8-wide vector of the group, so that each lane accumulates its two columns
+//     privately in the reference's order and the four lanes chain their totals with warp
+//     shuffles; min/max use xor-shuffles inside the quad.
+//   * compress_sym_stream_kernel: the plain symmetric codec has no search and is
+//     HBM-bound; 16 values per thread, one 256-bit load, one 128-bit store.
+// The reference's order of the sum (its CPU reduction): vectors of 8 lanes, four partial
+// accumulators per lane over runs of four vectors, left-over vectors into accumulator 0,
+// accumulators combined in order, then the 8 lane totals left to right.
 //
 // Exactness rules (src/tensorcache/codec.py:833-893 and :721-771):
 //   every operation is a separate IEEE binary32 operation -- __fdiv_rn / __fmul_rn /
 //   __fadd_rn / __fsub_rn (never contracted into FMA), rintf() for
 //   round-half-to-even, the first minimum wins (strict <), and the candidate
 //   multipliers are the host's torch.linspace values passed in by value.
-// The kernels are ALU-bound (~12 dependent fp32 operations per value and candidate).
-// The reference's per-value IEEE division x / s is replaced by a multiplication with the
-// candidate's reciprocal plus a guard that falls back to the exact division in the rare
-// case where the two could round to different codes (see quant_index), so the result is
-// still the reference's, bit for bit.  The kernels never synchronise with the host.
+// The kernels are ALU-bound (~14 thread instructions per value and candidate).
+// The reference's per-value IEEE division x / s is computed as the exact IEEE quotient
+// from the candidate's reciprocal and two FMAs (exact_quotient; the lane kernels and the
+// quality search), or as a reciprocal multiply plus a guard that falls back to the real
+// division in the rare case where the two could round to different codes (quant_index;
+// the quad kernels' table presets), so the result is still the reference's, bit for bit.
+// The kernels never synchronise with the host.
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -937,18 +952,20 @@ compress_sym_stream_kernel(const T* __restrict__ x, int64_t units, uint8_t* __re
 
 template <int LPG, typename T>
 cudaError_t launch_sym_stream(const void* x, int64_t groups, uint8_t* q, uint16_t* scales, cudaStream_t st) {
-    static int blocks_cache[64] = {0};
+    static std::atomic<int> blocks_cache[64];   // zero-initialised; the look-up is idempotent
     int dev = 0;
     int resident = tcb::sm_count() * 4;
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
-        if (blocks_cache[dev] == 0) {
+        int have = blocks_cache[dev].load(std::memory_order_relaxed);
+        if (have == 0) {
             int per_sm = 0;
             if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, compress_sym_stream_kernel<LPG, T>, kThreads, 0) != cudaSuccess ||
                 per_sm < 1)
                 per_sm = 4;
-            blocks_cache[dev] = per_sm * tcb::sm_count();
+            have = per_sm * tcb::sm_count();
+            blocks_cache[dev].store(have, std::memory_order_relaxed);
         }
-        resident = blocks_cache[dev];
+        resident = have;
     }
     const int64_t units = groups * LPG;
     int64_t grid = resident;  // one wave; small inputs get fewer, fuller blocks

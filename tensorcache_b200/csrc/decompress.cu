@@ -29,6 +29,8 @@
 // and 48 take a kernel that owns 8 codes per thread (no group straddles an octet).
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "tcb_common.h"
 
 namespace {
@@ -357,21 +359,36 @@ decompress_scalar_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
     }
 }
 
-// Blocks of `kernel` one device holds at once (occupancy x SM count), cached per device.
+// Blocks of `kernel` one device holds at once (occupancy x SM count), cached per device.  The look-up is
+// idempotent, so concurrent first calls may both do it; the cache word itself is atomic.
+typedef std::atomic<int> WaveCache[64];
+
 template <typename K>
-int resident_blocks(K kernel, int* cache) {
+int resident_blocks(K kernel, WaveCache& cache) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return tcb::sm_count() * 4;
-    if (cache[dev] == 0) {
+    int have = cache[dev].load(std::memory_order_relaxed);
+    if (have == 0) {
         int per_sm = 0;
         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
-        cache[dev] = per_sm * tcb::sm_count();
+        have = per_sm * tcb::sm_count();
+        cache[dev].store(have, std::memory_order_relaxed);
     }
-    return cache[dev];
+    return have;
 }
 
+// The per-device wave sizes of the power-of-two kernels, outside the launch functions so that they can be filled ahead of time.
+template <int LOG2_G, bool SYM>
+struct AlignedWaves {
+    static WaveCache v8, vec;
+};
+template <int LOG2_G, bool SYM>
+WaveCache AlignedWaves<LOG2_G, SYM>::v8;
+template <int LOG2_G, bool SYM>
+WaveCache AlignedWaves<LOG2_G, SYM>::vec;
+
 template <typename K, typename QPtr>
-cudaError_t launch_one_wave(K kernel, int* cache, int64_t units, QPtr q, const uint16_t* s, const uint8_t* zp, uint16_t* out,
+cudaError_t launch_one_wave(K kernel, WaveCache& cache, int64_t units, QPtr q, const uint16_t* s, const uint8_t* zp, uint16_t* out,
                             int64_t numel, cudaStream_t st) {
     int64_t grid = resident_blocks(kernel, cache);
     const int64_t min_units_per_block = kThreads;  // small inputs: fewer, fuller blocks
@@ -393,16 +410,29 @@ cudaError_t launch_one_wave(K kernel, int* cache, int64_t units, QPtr q, const u
 template <int LOG2_G, bool SYM>
 cudaError_t launch_aligned(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel,
                            bool aligned32, cudaStream_t st) {
-    static int cache32[64] = {0}, cache16[64] = {0};
-    if (aligned32) return launch_one_wave(decompress_v8_kernel<LOG2_G, SYM>, cache32, numel >> 5, q, s, zp, out, numel, st);
-    return launch_one_wave(decompress_vec_kernel<LOG2_G - 4, SYM>, cache16, numel >> 4, reinterpret_cast<const uint4*>(q), s,
-                           zp, out, numel, st);
+    if (aligned32)
+        return launch_one_wave(decompress_v8_kernel<LOG2_G, SYM>, AlignedWaves<LOG2_G, SYM>::v8, numel >> 5, q, s, zp, out, numel, st);
+    return launch_one_wave(decompress_vec_kernel<LOG2_G - 4, SYM>, AlignedWaves<LOG2_G, SYM>::vec, numel >> 4,
+                           reinterpret_cast<const uint4*>(q), s, zp, out, numel, st);
+}
+
+// Loads the kernels of one group size (all three output-alignment classes) onto the current device and fills
+// their wave sizes, without launching anything.
+template <int LOG2_G>
+cudaError_t prime_amo_variants() {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, decompress_v8_kernel<LOG2_G, false>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, decompress_vec_kernel<LOG2_G - 4, false>);
+    if (e != cudaSuccess) return e;
+    (void)resident_blocks(decompress_v8_kernel<LOG2_G, false>, AlignedWaves<LOG2_G, false>::v8);
+    (void)resident_blocks(decompress_vec_kernel<LOG2_G - 4, false>, AlignedWaves<LOG2_G, false>::vec);
+    return cudaSuccess;
 }
 
 template <int OPG, bool SYM>
 cudaError_t launch_oct(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel, bool aligned32,
                        cudaStream_t st) {
-    static int cache[64] = {0}, cache32[64] = {0};
+    static WaveCache cache, cache32;
     if (aligned32) return launch_one_wave(decompress_v8_oct_kernel<OPG, SYM>, cache32, numel >> 5, q, s, zp, out, numel, st);
     return launch_one_wave(decompress_oct_kernel<OPG, SYM>, cache, numel >> 3, reinterpret_cast<const uint2*>(q), s, zp, out,
                            numel, st);
@@ -438,6 +468,18 @@ int launch_any(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint
 }  // namespace
 
 namespace tcb {
+
+// Makes every kernel the AMO-BQ decode of G = 16 / 32 / 64 can pick (whatever the output's alignment) resident on
+// the current device, so that a later launch loads no module and asks no occupancy question.
+cudaError_t prime_amo_decompress() {
+    cudaFuncAttributes fa;
+    cudaError_t e = prime_amo_variants<4>();
+    if (e == cudaSuccess) e = prime_amo_variants<5>();
+    if (e == cudaSuccess) e = prime_amo_variants<6>();
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, decompress_scalar_kernel<false>);
+    (void)sm_count();
+    return e;
+}
 
 // Shared by the public entry points and the streamer.  zp == nullptr selects the symmetric codec.
 int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,

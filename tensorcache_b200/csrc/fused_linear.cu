@@ -8,31 +8,56 @@
 // memory tile the tensor core reads (the canonical K-major, 128-byte-swizzled
 // UMMA operand layout).  The dense operand arrives by TMA into the same layout.
 //
-// One CTA per SM, persistent over output tiles of 128 (quantised rows) x 256
-// (dense rows); K advances 64 at a time through a 3-stage ring.
-//   warp 0      TMA producer: dense tile [256 x 64] bf16 and raw code tile [128 x 64]
-//               uint8 per stage (one thread)
-//   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K16) per stage, commits
-//               the stage back to the producers and the finished accumulator to
-//               the epilogue (one thread); also owns the TMEM allocation
-//   warps 2-9   dequantising producers: read the raw codes from shared memory,
-//               write 128 rows x 64 bf16 per stage; scales / zero points come from a
-//               double-buffered shared-memory chunk (32 groups per row) that the
-//               producers refill themselves one chunk ahead.  (Fetching codes and
-//               scales with per-thread global loads instead capped the kernel at
-//               ~740 TFLOP/s: the LSU miss path, not the math, was the limit.)
-//   warps 10-13 epilogue: tcgen05.ld -> (+bias) -> bf16 -> global
-// The 512 TMEM columns hold two 128 x 256 fp32 accumulators, so the epilogue of
-// one tile overlaps the main loop of the next.  No TMA multicast, no cluster.
+// The kernel runs as pairs of CTAs (a cluster of two, one CTA per SM of a TPC) that
+// issue tcgen05.mma.cta_group::2: one 256 x 256 output tile per pair, K advancing 64
+// at a time through a 5-stage ring.  Each CTA of the pair dequantises 128 rows of the
+// quantised operand and loads 128 rows of the dense one; the tensor cores of the two
+// SMs exchange the halves of the N-side operand between themselves, so per flop each
+// SM moves a third fewer operand bytes through its shared memory than a single-CTA
+// 128 x 256 tile does.  That matters because the shared-memory data pipe (one 128-byte
+// wavefront per clock), not the tensor pipe, is what bounds this kernel: per K step it
+// serves the tensor core's operand reads (256 wavefronts), the TMA's writes (192) and
+// the producers' loads and stores (about 270), against the 512 clocks the step's MMAs take.
 //
-// The dequantised value is bf16((q - zp) * scale): q - zp is formed exactly in
-// fp32, rounded to bf16 without error (|q - zp| <= 255 fits 8 significant bits)
-// and multiplied by the bf16 scale with one correctly rounded bf16 multiply, i.e.
-// it is the same number the decode kernel produces.
+// Which operand is the M side depends on the wanted output layout, so that every
+// epilogue store is a row-contiguous vector store:
+//     quant_is_rhs (out = dense . deq(q)^T, [R_d, R_q]):  A = dense, B = dequantised
+//     otherwise    (out = deq(q) . dense^T, [R_q, R_d]):  A = dequantised, B = dense
+// The per-CTA work is the same in both cases.
+//
+// Warp roles, per CTA:
+//   warp 0      TMA producer (one thread): raw code tile [128 x 64] uint8 into the CTA's
+//               own barrier, dense tile [128 x 64] bf16 (128-byte swizzle) into the
+//               leader CTA's barrier (cp.async.bulk.tensor with cta_group::2, no multicast)
+//   warp 1      leader CTA only, one thread: per stage ONE barrier wait (dense halves of both
+//               CTAs landed + all 16 producer warps of the pair done), 4 x tcgen05.mma
+//               (M256 N256 K16) and ONE tcgen05.commit that arrives on the stage barrier of
+//               both CTAs; after the last K step one more on both accumulator barriers.
+//               This thread's serial latency per stage is on the critical path, hence the
+//               merged barrier and the single commit.  In both CTAs this warp owns the
+//               TMEM allocation.
+//   warps 2-9   dequantising producers: 16 rows per warp.  A warp instruction reads 512
+//               contiguous bytes of codes and writes 16-byte pieces that cover all 32
+//               banks per quarter warp, so neither side has bank conflicts.  Scales and
+//               zero points sit merged (scale << 16 | zp) in a per-warp shared-memory
+//               table of 32 groups per row that the warp refills itself one table ahead
+//               (global -> registers -> table), so a turn-over needs only a warp sync.
+//   warps 10-13 epilogue: tcgen05.ld -> (+bias) -> bf16 -> global (32-byte stores)
+// The 512 TMEM columns hold two 256-column fp32 accumulators, so the epilogue of
+// one tile overlaps the main loop of the next.  No TMA multicast anywhere.
+//
+// The dequantised value is bf16((q - zp) * scale), the number the decode kernel produces:
+// the code byte is spliced into the mantissa of 2^15, one FMA with the exact constant
+// -(2^15 + zp) * scale yields (q - zp) * scale exactly in fp32 (16 x 8 significant
+// bits), and cvt.rn.bf16x2.f32 rounds two of them once.
 //
 // Every wait on an mbarrier is bounded by a clock budget.  When one runs out the
-// thread raises a CTA-wide abort flag and a device status word; all roles leave
-// their loops, the CTA synchronises, frees its TMEM and returns.
+// thread raises the abort flag of both CTAs of the pair and a device status word; all
+// roles leave their loops, the pair synchronises, frees its TMEM and returns.  Nothing
+// in the kernel blocks without such a bound (in particular no setmaxnreg, whose .inc
+// form waits for registers another warp group has to give up).
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -40,27 +65,24 @@
 
 namespace {
 
-constexpr int kTileQ = 128;      // rows of the quantised operand per tile (MMA M)
-constexpr int kTileD = 256;      // rows of the dense operand per tile (MMA N)
+constexpr int kTileRows = 128;   // rows of each operand per CTA and tile
+constexpr int kPairRows = 256;   // rows of each operand per CTA pair and tile (MMA M = N = 256)
 constexpr int kBlockK = 64;      // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kStages = 3;
+constexpr int kStages = 5;
 constexpr int kNumProducerWarps = 8;
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 448
 constexpr int kFirstProducerWarp = 2;
 constexpr int kFirstEpilogueWarp = 2 + kNumProducerWarps;                   // 10
-constexpr uint32_t kStageBytesA = kTileQ * kBlockK * 2;                      // 16 KB
-constexpr uint32_t kStageBytesB = kTileD * kBlockK * 2;                      // 32 KB
-constexpr uint32_t kStageBytesC = kTileQ * kBlockK;                          // 8 KB of raw codes
-constexpr int kChunkGroups = 32;                                             // groups per row per scale chunk
-constexpr uint32_t kChunkBytesS = kTileQ * kChunkGroups * 2;                 // 8 KB of bf16 scales
-constexpr uint32_t kChunkBytesZ = kTileQ * kChunkGroups;                     // 4 KB of zero points
-constexpr uint32_t kSmemTiles = kStages * (kStageBytesA + kStageBytesB + kStageBytesC) + 2 * (kChunkBytesS + kChunkBytesZ);
+constexpr uint32_t kStageBytesQ = kTileRows * kBlockK * 2;                   // 16 KB dequantised operand
+constexpr uint32_t kStageBytesD = kTileRows * kBlockK * 2;                   // 16 KB dense operand
+constexpr uint32_t kStageBytesC = kTileRows * kBlockK;                       // 8 KB of raw codes
+constexpr int kTableGroups = 32;                                             // groups per row in the scale table
+constexpr uint32_t kTableRowBytes = kTableGroups * 4 + 16;                   // 144: the pad spreads 8 rows over all banks
+constexpr uint32_t kTableBytes = kTileRows * kTableRowBytes;                 // 18 KB
+constexpr uint32_t kSmemTiles = kStages * (kStageBytesQ + kStageBytesD + kStageBytesC) + kTableBytes;
 constexpr uint32_t kSmemBytes = kSmemTiles + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr long long kWaitBudgetClocks = 4000000000LL;  // ~2 s at 2 GHz
-constexpr uint32_t kSuspendHintNs = 20000;              // a waiting thread may sleep this long inside one try_wait
-                                                       // (it is woken when the phase completes), so waiters do not
-                                                       // burn issue slots the producer warps need
+constexpr long long kWaitBudgetClocks = 2000000000LL;  // ~1 s at 2 GHz
 
 __device__ int g_status = 0;  // 0 ok; otherwise (role << 8 | barrier id) of the first wait that ran out
 
@@ -68,29 +90,52 @@ __device__ int g_status = 0;  // 0 ok; otherwise (role << 8 | barrier id) of the
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+// Arrival on a barrier that may live in the other CTA of the pair (shared::cluster address).  The plain form: with
+// .release.cluster on every arrival the arriving warp stalled for about a thousand clocks per stage.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One poll of a barrier phase.  Cluster-scope acquire: most of these barriers take arrivals from the other CTA of
+// the pair or from MMAs both CTAs take part in.  No suspend-time hint: it made no difference here.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
 
-// Bounded wait.  Returns false if the CTA is aborting (or this wait ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who,
+// Bounded wait.  Returns false if the CTA pair is aborting (or this wait ran out).  `abort_peer` is the
+// shared::cluster address of the other CTA's abort flag (0: no pair).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t abort_peer, int who,
                                           long long budget = kWaitBudgetClocks) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -101,6 +146,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (*abort_flag) return false;
         if (clock64() - t0 > budget) {
             *abort_flag = 1;
+            if (abort_peer) st_cluster_u32(abort_peer, 1u);
             atomicCAS(&g_status, 0, who);
             return false;
         }
@@ -113,30 +159,42 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
 }
+// Load into this CTA's shared memory that signals a barrier of either CTA of the pair
+// (`cluster_bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+        : "memory");
+}
 
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
 }
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+// Arrival on the barrier at offset `bar` of BOTH CTAs of the pair once every MMA this thread has issued so far has completed.
+__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(uint16_t(3))
+                 : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -152,6 +210,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+
 // K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -163,63 +227,40 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
-// bf16 x bf16 -> fp32, A and B K-major, M = 128, N = 256
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileD >> 3) << 17) | (uint32_t(kTileQ >> 4) << 24);
+// bf16 x bf16 -> fp32, A and B K-major, M = 256 (128 rows per CTA of the pair), N = 256
+constexpr uint32_t kInstrDesc =
+    (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kPairRows >> 3) << 17) | (uint32_t(kPairRows >> 4) << 24);
 
 // ------------------------------------------------------------------- dequant
-
-__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-
-// 4 code bytes -> 4 bf16 values (q - zp) * scale, packed as two bf16x2
-__device__ __forceinline__ void dequant_word(uint32_t w, float zmagic, uint32_t scale2, uint32_t& o0, uint32_t& o1) {
-    const uint32_t magic = 0x4B000000u;  // 2^23: the byte lands in the low mantissa bits
-    const float f0 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7650)), zmagic);
-    const float f1 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7651)), zmagic);
-    const float f2 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7652)), zmagic);
-    const float f3 = __fsub_rn(__uint_as_float(__byte_perm(w, magic, 0x7653)), zmagic);
-    // |q - zp| <= 255 has at most 8 significant bits, so the upper half of the fp32
-    // pattern IS the bf16 value: pack by byte permute, no conversion instruction
-    const uint32_t p0 = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-    const uint32_t p1 = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
-    o0 = bf16x2_mul(p0, scale2);
-    o1 = bf16x2_mul(p1, scale2);
-}
 
 struct Params {
     const uint8_t* q;         // [R_q, K]
     const uint16_t* scales;   // [R_q * K / G]
     const uint8_t* zp;        // same, or null: codes are signed int8
-    const uint16_t* bias;     // null, or [R_d] (natural layout) / [R_q] (transposed output)
-    uint16_t* out;            // natural: [R_q, R_d]; transposed: [R_d, R_q]
+    const uint16_t* bias;     // null, or one entry per output column
+    uint16_t* out;            // [rows of the A operand, rows of the B operand]
     int64_t R_q, R_d, K;
     int64_t gpr;              // groups per row = K / G
-    int chunk_vec_ok;         // scales / zero points of a chunk can be fetched with 16-byte loads
-    int log2_g;
-    int transpose_out;
-    int tiles_q, tiles_d;
+    int table_vec_ok;         // scales / zero points of a table can be fetched with 16-byte loads
+    int quant_is_a;           // the dequantised operand is the M side (output rows); otherwise the dense one is
+    int tiles_q, tiles_d;     // pair tiles (256 rows) along each operand
 };
 
-// Scales and zero points reach the producers through a small shared-memory
-// buffer that covers 32 groups per row ("a chunk": 512 / 1024 / 2048 values of K for
-// G = 16 / 32 / 64).  Thread (row, half) of the 256 producers fetches groups
-// [16 * half, 16 * half + 16) of its row into registers one chunk ahead and spills
-// them into the other half of the double buffer when the chunk turns over.  Per
-// stage the producers then need only two shared-memory reads instead of two
-// sector-wasting global loads, which keeps the LSU miss path almost idle.
-struct ChunkRegs {
+// Scales and zero points reach the producers through a shared-memory table that covers
+// 32 groups per row (512 / 1024 / 2048 values of K for G = 16 / 32 / 64), one 32-bit word
+// (scale << 16 | zp) per group.  Each producer warp owns the 16 rows it converts: lane
+// (row = lane / 2, half = lane % 2) fetches groups [16 * half, 16 * half + 16) of its row
+// into registers one table ahead and writes them out when the table turns over.
+struct TableRegs {
     uint4 s0, s1;  // 16 bf16 scales
     uint4 z;       // 16 zero points
 };
 
-__device__ __forceinline__ void chunk_fetch(const Params& p, int64_t grow, int64_t g_first, bool row_ok, ChunkRegs& c) {
+__device__ __forceinline__ void table_fetch(const Params& p, int64_t grow, int64_t g_first, bool row_ok, TableRegs& c) {
     c.s0 = c.s1 = c.z = make_uint4(0, 0, 0, 0);
     if (!row_ok || g_first >= p.gpr) return;
     const int64_t base = grow * p.gpr + g_first;
-    if (p.chunk_vec_ok && g_first + 16 <= p.gpr) {
+    if (p.table_vec_ok && g_first + 16 <= p.gpr) {
         const uint4* sp = reinterpret_cast<const uint4*>(p.scales + base);
         c.s0 = __ldg(sp);
         c.s1 = __ldg(sp + 1);
@@ -238,48 +279,56 @@ __device__ __forceinline__ void chunk_fetch(const Params& p, int64_t grow, int64
     c.z = make_uint4(zw[0], zw[1], zw[2], zw[3]);
 }
 
-__device__ __forceinline__ void chunk_spill(uint8_t* sbuf, uint8_t* zbuf, int row, int half, const ChunkRegs& c) {
-    uint4* sd = reinterpret_cast<uint4*>(sbuf + row * (kChunkGroups * 2) + half * 32);
-    sd[0] = c.s0;
-    sd[1] = c.s1;
-    *reinterpret_cast<uint4*>(zbuf + row * kChunkGroups + half * 16) = c.z;
+// Writes the 16 (scale, zero point) pairs a lane holds as 16 merged words: bytes 3..2 = scale, byte 0 = zp.
+__device__ __forceinline__ void table_spill(uint8_t* dst, const TableRegs& c) {
+    const uint32_t sw[8] = {c.s0.x, c.s0.y, c.s0.z, c.s0.w, c.s1.x, c.s1.y, c.s1.z, c.s1.w};
+    const uint32_t zw[4] = {c.z.x, c.z.y, c.z.z, c.z.w};
+    uint32_t m[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        // selector nibbles, low to high: zp byte (e & 3) of zw, the same again, scale bytes (2 (e & 1), 2 (e & 1) + 1) of sw
+        const uint32_t zsel = 4 + (e & 3), ssel = 2 * (e & 1);
+        m[e] = __byte_perm(sw[e >> 1], zw[e >> 2], zsel | (zsel << 4) | (ssel << 8) | ((ssel + 1) << 12));
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = make_uint4(m[4 * v], m[4 * v + 1], m[4 * v + 2], m[4 * v + 3]);
 }
 
-// One producer thread's share of a stage: row `row` of the tile, codes [32 * half, 32 * half + 32).
-// Reads the raw codes the TMA delivered (rows of 64 bytes), dequantises them and writes four
-// 16-byte chunks of bf16 into the 128-byte-swizzled A tile.  All addresses are a per-thread base
-// (computed once, outside the main loop) plus compile-time offsets; `srow` / `zrow` point at the
-// scale / zero point of the thread's first code in the current chunk buffer.
-template <int LOG2_G, bool HAS_ZP>
-__device__ __forceinline__ void producer_convert(const uint8_t* c_thread, uint8_t* a_row, const uint32_t (&chunk_off)[4],
-                                                 const uint16_t* srow, const uint8_t* zrow) {
-    const uint4 c0 = *reinterpret_cast<const uint4*>(c_thread);
-    const uint4 c1 = *reinterpret_cast<const uint4*>(c_thread + 16);
-    uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-    constexpr bool kTwoGroups = LOG2_G == 4;  // G = 16: the thread's 32 codes span two groups
-    uint32_t sb[2], zv[2];
-    sb[0] = srow[0];
-    sb[1] = kTwoGroups ? uint32_t(srow[1]) : sb[0];
+// 16 codes of one row -> 16 bf16 values, written as two 16-byte pieces of the 128-byte-swizzled operand row.
+// Per code: one byte permute (the byte into the mantissa of 2^15), one FMA, half a cvt.rn.bf16x2.f32.
+template <bool HAS_ZP>
+__device__ __forceinline__ void convert16(uint4 c, uint32_t sz_word, uint8_t* piece0, uint8_t* piece1) {
+    uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    const float scale = __uint_as_float(sz_word & 0xFFFF0000u);
+    float base;
     if (HAS_ZP) {
-        zv[0] = zrow[0];
-        zv[1] = kTwoGroups ? uint32_t(zrow[1]) : zv[0];
-    } else {  // signed codes: flip the sign bit and subtract 128
+        base = __uint_as_float(__byte_perm(sz_word, 0x47000000u, 0x7604));
+    } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) words[i] ^= 0x80808080u;
-        zv[0] = zv[1] = 128;
+        for (int i = 0; i < 4; ++i) w[i] ^= 0x80808080u;
+        base = __uint_as_float(0x47008000u);
     }
+    const float cc = -__fmul_rn(base, scale);
+    const uint32_t magic = 0x47000000u;
+    uint32_t o[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {  // chunk j of this half: codes 8j .. 8j+7
-        const int h = j >> 1;
-        const float zmagic = __uint_as_float(0x4B000000u | zv[h]);  // 2^23 + zp, exact
-        const uint32_t s2 = __byte_perm(sb[h], sb[h], 0x1010);      // the scale in both halves
-        uint4 o;
-        dequant_word(words[2 * j], zmagic, s2, o.x, o.y);
-        dequant_word(words[2 * j + 1], zmagic, s2, o.z, o.w);
-        *reinterpret_cast<uint4*>(a_row + chunk_off[j]) = o;
+    for (int i = 0; i < 4; ++i) {
+        const float f0 = __fmaf_rn(__uint_as_float(__byte_perm(w[i], magic, 0x7604)), scale, cc);
+        const float f1 = __fmaf_rn(__uint_as_float(__byte_perm(w[i], magic, 0x7614)), scale, cc);
+        const float f2 = __fmaf_rn(__uint_as_float(__byte_perm(w[i], magic, 0x7624)), scale, cc);
+        const float f3 = __fmaf_rn(__uint_as_float(__byte_perm(w[i], magic, 0x7634)), scale, cc);
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[2 * i]) : "f"(f1), "f"(f0));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[2 * i + 1]) : "f"(f3), "f"(f2));
     }
+    *reinterpret_cast<uint4*>(piece0) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(piece1) = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+}
 __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
     __nv_bfloat16 b = __float2bfloat16_rn(v);
     return *reinterpret_cast<uint16_t*>(&b);
@@ -288,142 +337,151 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
 // -------------------------------------------------------------------- kernel
 
 template <int LOG2_G, bool HAS_ZP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const __grid_constant__ CUtensorMap code_map, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* smem_a = smem;                                   // kStages x 16 KB, dequantised operand
-    uint8_t* smem_b = smem + kStages * kStageBytesA;          // kStages x 32 KB, dense operand (TMA)
-    uint8_t* smem_c = smem_b + kStages * kStageBytesB;        // kStages x 8 KB, raw codes (TMA)
-    uint8_t* smem_s = smem_c + kStages * kStageBytesC;        // 2 x 8 KB, scales of the current / next chunk
-    uint8_t* smem_z = smem_s + 2 * kChunkBytesS;              // 2 x 4 KB, zero points
+    uint8_t* smem_q = smem;                                   // kStages x 16 KB, dequantised operand
+    uint8_t* smem_d = smem + kStages * kStageBytesQ;          // kStages x 16 KB, dense operand (TMA)
+    uint8_t* smem_c = smem_d + kStages * kStageBytesD;        // kStages x 8 KB, raw codes (TMA)
+    uint8_t* smem_t = smem_c + kStages * kStageBytesC;        // 18 KB, scale / zero point tables of the 8 producer warps
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemTiles);
-    // barrier ids: [0,S) full_b, [S,2S) full_a, [2S,3S) empty, [3S,4S) full_c, 4S+{0,1} tmem_full, 4S+{2,3} tmem_empty,
-    // 4S+4 chunk turn-over among the producers
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 5);
+    // barrier ids: [0,S) full, [S,2S) empty, [2S,3S) full_c, 3S+{0,1} tmem_full, 3S+{2,3} tmem_empty.
+    // full and tmem_empty are used in the leader CTA only (the other CTA arrives on them remotely).
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kStages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();   // 0: leader (issues the MMAs)
+    const bool leader = rank == 0;
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int id) { return bar0 + 8u * uint32_t(id); };
-    const int FULL_B = 0, FULL_A = kStages, EMPTY = 2 * kStages, FULL_C = 3 * kStages, TFULL = 4 * kStages, TEMPTY = 4 * kStages + 2,
-              CHUNK = 4 * kStages + 4;
+    auto leader_bar = [&](int id) { return map_to_cta(bar(id), 0); };
+    const uint32_t abort_peer = map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1);
+    const int FULL = 0, EMPTY = kStages, FULL_C = 2 * kStages, TFULL = 3 * kStages, TEMPTY = 3 * kStages + 2;
 
+    // both CTAs of the pair are resident before either touches the other's shared or tensor memory
+    cluster_sync_all();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar(FULL_B + s), 1);
-            mbar_init(bar(FULL_A + s), kNumProducerWarps * 32);
+            mbar_init(bar(FULL + s), 2 + 2 * kNumProducerWarps);
             mbar_init(bar(EMPTY + s), 1);
             mbar_init(bar(FULL_C + s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(TFULL + b), 1);
-            mbar_init(bar(TEMPTY + b), kNumEpilogueWarps * 32);
+            mbar_init(bar(TEMPTY + b), 2 * kNumEpilogueWarps * 32);
         }
-        mbar_init(bar(CHUNK), kNumProducerWarps * 32);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        tmem_alloc_pair(smem_u32(tmem_slot), 512);
+        tmem_relinquish_pair();
     }
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_kb = int((p.K + kBlockK - 1) / kBlockK);  // a ragged last K block is zero-filled by the TMA (dense tile and
-                                                            // codes) and gets zero scales from the chunk fetch
+                                                            // codes) and gets zero scales from the table fetch
     const int num_tiles = p.tiles_q * p.tiles_d;
+    const int first_tile = int(blockIdx.x >> 1), tile_step = int(gridDim.x >> 1);
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (dense operand and raw codes)
         if (lane == 0) {
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
                 const int td = tile % p.tiles_d, tq = tile / p.tiles_d;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, (1 << 8) | (EMPTY + s)))) break;
+                const int q_row = tq * kPairRows + int(rank) * kTileRows, d_row = td * kPairRows + int(rank) * kTileRows;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, abort_peer, (1 << 8) | (EMPTY + s));
+                    if (!ok) break;
                     mbar_arrive_expect_tx(bar(FULL_C + s), kStageBytesC);
-                    tma_load_2d(smem_u32(smem_c + s * kStageBytesC), &code_map, kb * kBlockK, tq * kTileQ, bar(FULL_C + s));
-                    mbar_arrive_expect_tx(bar(FULL_B + s), kStageBytesB);
-                    tma_load_2d(smem_u32(smem_b + s * kStageBytesB), &dense_map, kb * kBlockK, td * kTileD, bar(FULL_B + s));
+                    tma_load_2d(smem_u32(smem_c + s * kStageBytesC), &code_map, kb * kBlockK, q_row, bar(FULL_C + s));
+                    const uint32_t fd = leader_bar(FULL + s);
+                    tma_load_2d_pair(smem_u32(smem_d + s * kStageBytesD), &dense_map, kb * kBlockK, d_row, fd);
+                    if (leader)
+                        mbar_arrive_expect_tx(bar(FULL + s), 2 * kStageBytesD);
+                    else
+                        mbar_arrive_cluster(fd);
+                    if (++s == kStages) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0, local_tile = 0;
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            int s = 0;
+            uint32_t ph = 0, local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+            const uint8_t* smem_a = p.quant_is_a ? smem_q : smem_d;
+            const uint8_t* smem_b = p.quant_is_a ? smem_d : smem_q;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++local_tile) {
                 const int buf = local_tile & 1;
                 const uint32_t tph = (local_tile >> 1) & 1;
-                if (!(ok = mbar_wait(bar(TEMPTY + buf), tph ^ 1, abort_flag, (2 << 8) | (TEMPTY + buf)))) break;
+                ok = mbar_wait(bar(TEMPTY + buf), tph ^ 1, abort_flag, abort_peer, (2 << 8) | (TEMPTY + buf));
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + uint32_t(buf * kTileD);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % kStages;
-                    const uint32_t ph = (it / kStages) & 1;
-                    if (!(ok = mbar_wait(bar(FULL_B + s), ph, abort_flag, (2 << 8) | (FULL_B + s)))) break;
-                    if (!(ok = mbar_wait(bar(FULL_A + s), ph, abort_flag, (2 << 8) | (FULL_A + s)))) break;
+                const uint32_t d_tmem = tmem_base + uint32_t(buf * kPairRows);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(bar(FULL + s), ph, abort_flag, abort_peer, (2 << 8) | (FULL + s));
+                    if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesA);
-                    const uint32_t b_addr = smem_u32(smem_b + s * kStageBytesB);
+                    const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesQ);
+                    const uint32_t b_addr = smem_u32(smem_b + s * kStageBytesQ);
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k)
-                        umma_bf16(d_tmem, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), kInstrDesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar(EMPTY + s));  // the stage may be refilled once these MMAs have read it
+                        umma_bf16_pair(d_tmem, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), kInstrDesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                    // the stage may be refilled, in both CTAs, once these MMAs have read it
+                    umma_commit_both(bar(EMPTY + s));
+                    if (++s == kStages) { s = 0; ph ^= 1; }
                 }
-                if (ok) umma_commit(bar(TFULL + buf));  // accumulator complete
+                if (ok) {  // accumulator complete: each CTA's epilogue reads its own 128 rows
+                    umma_commit_both(bar(TFULL + buf));
+                }
             }
         }
     } else if (warp < kFirstEpilogueWarp) {
         // ------------------------------------------------ dequantising producers
-        // Per stage: wait for the raw codes (which the TMA thread only requests once the
-        // stage's previous MMAs have released it), convert, publish.  Scales and zero
-        // points come from the chunk buffer; the registers for the next chunk are
-        // fetched one chunk ahead, across tile boundaries too.
-        const int pt = threadIdx.x - kFirstProducerWarp * 32;  // 0..255
-        const int row = pt >> 1, half = pt & 1;
-        constexpr int kLog2Cs = LOG2_G - 1;                    // stages per chunk = 32 * G / 64
-        constexpr int kCsMask = (1 << kLog2Cs) - 1;
-        const int chunks_per_tile = (num_kb + kCsMask) >> kLog2Cs;
-        // per-thread addresses, fixed for the whole kernel
-        const uint8_t* c_thread = smem_c + row * kBlockK + half * 32;               // + stage * kStageBytesC
-        uint8_t* a_row = smem_a + (row >> 3) * 1024 + (row & 7) * 128;               // + stage * kStageBytesA
-        uint32_t chunk_off[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) chunk_off[j] = uint32_t(((half * 4 + j) ^ (row & 7)) * 16);
-        // group (inside a chunk) of the thread's first code at stage j of the chunk:
-        // G16: 4 j + 2 half, G32: 2 j + half, G64: j
-        constexpr int kGroupsPerStage = 64 >> LOG2_G;                                // 4, 2, 1
-        const int g_half = LOG2_G == 4 ? 2 * half : (LOG2_G == 5 ? half : 0);
-        const uint8_t* s_thread = smem_s + row * (kChunkGroups * 2) + g_half * 2;   // + buf * kChunkBytesS + j * groups * 2
-        const uint8_t* z_thread = smem_z + row * kChunkGroups + g_half;             // + buf * kChunkBytesZ + j * groups
-        // cursor of the chunk prefetch: (tile, chunk inside the tile)
-        int pf_tile = blockIdx.x, pf_chunk = 0;
-        ChunkRegs regs;
-        auto fetch_next_chunk = [&]() {
+        // Per stage: wait for the raw codes (which the TMA thread only requests once the stage's
+        // previous MMAs have released it), convert, publish to the leader's barrier.
+        const int pw = warp - kFirstProducerWarp;              // 0..7: rows [16 pw, 16 pw + 16) of the CTA's tile
+        constexpr int kLog2Ts = LOG2_G - 1;                    // stages per table = 32 * G / 64
+        constexpr int kTsMask = (1 << kLog2Ts) - 1;
+        constexpr int kGroupsPerStage = 64 >> LOG2_G;          // 4, 2, 1
+        const int tables_per_tile = (num_kb + kTsMask) >> kLog2Ts;
+        // conversion role of this lane: 16 codes at quarter kq of rows ra and ra + 8
+        const int ra = pw * 16 + (lane >> 2), kq = lane & 3;
+        const uint8_t* c_lane = smem_c + ra * kBlockK + kq * 16;                        // + stage * kStageBytesC; second row: + 512
+        uint8_t* q_row = smem_q + (ra >> 3) * 1024 + (ra & 7) * 128;                    // + stage * kStageBytesQ; second row: + 1024
+        const uint32_t piece0 = uint32_t(((2 * kq) ^ (ra & 7)) * 16), piece1 = piece0 ^ 16u;
+        const int g_sel = LOG2_G == 4 ? kq : (LOG2_G == 5 ? (kq >> 1) : 0);             // group of the lane's codes inside a stage
+        const uint8_t* t_lane = smem_t + ra * kTableRowBytes + g_sel * 4;               // + 4 * groups per stage * stage in table
+        // fetch role of this lane: row fr, groups [16 fh, 16 fh + 16) of the table
+        const int fr = pw * 16 + (lane >> 1), fh = lane & 1;
+        uint8_t* t_spill = smem_t + fr * kTableRowBytes + fh * 64;
+        int pf_tile = first_tile, pf_table = 0;
+        TableRegs regs;
+        auto fetch_next_table = [&]() {
             if (pf_tile < num_tiles) {
-                const int64_t grow = int64_t(pf_tile / p.tiles_d) * kTileQ + row;
-                chunk_fetch(p, grow, int64_t(pf_chunk) * kChunkGroups + half * 16, grow < p.R_q, regs);
+                const int64_t grow = int64_t(pf_tile / p.tiles_d) * kPairRows + int64_t(rank) * kTileRows + fr;
+                table_fetch(p, grow, int64_t(pf_table) * kTableGroups + fh * 16, grow < p.R_q, regs);
             }
-            if (++pf_chunk == chunks_per_tile) {
-                pf_chunk = 0;
-                pf_tile += gridDim.x;
+            if (++pf_table == tables_per_tile) {
+                pf_table = 0;
+                pf_tile += tile_step;
             }
         };
-        fetch_next_chunk();
-        const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+        fetch_next_table();
+        const int my_tiles = first_tile < num_tiles ? (num_tiles - 1 - first_tile) / tile_step + 1 : 0;
         const int64_t total = int64_t(my_tiles) * num_kb;
-        uint32_t gc = 0;      // chunks published so far
         uint32_t ph = 0;      // parity of the stage ring, flips once per kStages steps
         int kb = 0;           // k-block inside the current tile
         bool ok = true;
@@ -431,96 +489,99 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
 #pragma unroll
             for (int s = 0; s < kStages; ++s) {  // the stage index is a compile-time constant in here
                 if (i0 + s >= total) break;
-                const int j = kb & kCsMask;      // stage inside the chunk
+                const int j = kb & kTsMask;      // stage inside the table
                 if (j == 0) {
-                    // chunk turn-over: publish the prefetched registers, start fetching the next chunk
-                    const int nb = gc & 1;
-                    chunk_spill(smem_s + nb * kChunkBytesS, smem_z + nb * kChunkBytesZ, row, half, regs);
-                    fetch_next_chunk();
-                    // every producer must have spilled before anyone reads the new chunk (bounded, like all waits)
-                    mbar_arrive(bar(CHUNK));
-                    if (!(ok = mbar_wait(bar(CHUNK), gc & 1, abort_flag, (3 << 8) | CHUNK))) break;
-                    ++gc;
+                    // table turn-over, inside the warp: everybody has read the old words, write the prefetched
+                    // ones, start fetching the next table
+                    __syncwarp();
+                    table_spill(t_spill, regs);
+                    fetch_next_table();
+                    __syncwarp();
                 }
-                const int buf = (gc - 1) & 1;
-                if (!(ok = mbar_wait(bar(FULL_C + s), ph, abort_flag, (3 << 8) | (FULL_C + s)))) break;
-                producer_convert<LOG2_G, HAS_ZP>(
-                    c_thread + s * kStageBytesC, a_row + s * kStageBytesA, chunk_off,
-                    reinterpret_cast<const uint16_t*>(s_thread + buf * kChunkBytesS + j * (kGroupsPerStage * 2)),
-                    z_thread + buf * kChunkBytesZ + j * kGroupsPerStage);
-                fence_proxy_async();  // make the generic-proxy stores visible to the tensor core
-                mbar_arrive(bar(FULL_A + s));
+                const uint32_t sz_a = *reinterpret_cast<const uint32_t*>(t_lane + j * (kGroupsPerStage * 4));
+                const uint32_t sz_b = *reinterpret_cast<const uint32_t*>(t_lane + 8 * kTableRowBytes + j * (kGroupsPerStage * 4));
+                // the verdict of the wait is made warp-uniform: the warp-level syncs below need every lane
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL_C + s), ph, abort_flag, abort_peer, (3 << 8) | (FULL_C + s)));
+                if (!ok) break;
+                const uint4 ca = *reinterpret_cast<const uint4*>(c_lane + s * kStageBytesC);
+                const uint4 cb = *reinterpret_cast<const uint4*>(c_lane + s * kStageBytesC + 8 * kBlockK);
+                uint8_t* qa = q_row + s * kStageBytesQ;
+                convert16<HAS_ZP>(ca, sz_a, qa + piece0, qa + piece1);
+                convert16<HAS_ZP>(cb, sz_b, qa + 1024 + piece0, qa + 1024 + piece1);
+                fence_proxy_async();  // make this lane's generic-proxy stores visible to the tensor cores
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_bar(FULL + s));
                 if (++kb == num_kb) kb = 0;
             }
         }
     } else {
         // ------------------------------------------------ epilogue
         const int ew = warp & 3;                 // TMEM lane quadrant this warp may read
-        const int r_in_tile = ew * 32 + lane;    // accumulator row = quantised-operand row
+        const int r_in_tile = ew * 32 + lane;    // accumulator row of this CTA = row of the A operand
+        const int64_t rows_a = p.quant_is_a ? p.R_q : p.R_d, rows_b = p.quant_is_a ? p.R_d : p.R_q;
+        const bool out_vec = (rows_b % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(p.bias) & 3) == 0);
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local_tile) {
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++local_tile) {
             const int tq = tile / p.tiles_d, td = tile % p.tiles_d;
+            const int ta = p.quant_is_a ? tq : td, tb = p.quant_is_a ? td : tq;
             const int buf = local_tile & 1;
             const uint32_t tph = (local_tile >> 1) & 1;
-            if (!(ok = mbar_wait(bar(TFULL + buf), tph, abort_flag, (4 << 8) | (TFULL + buf)))) break;
+            // warp-uniform verdict: tcgen05.ld is a warp-wide instruction
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(TFULL + buf), tph, abort_flag, abort_peer, (4 << 8) | (TFULL + buf)));
+            if (!ok) break;
             tc_fence_after();
-            const int64_t rq = int64_t(tq) * kTileQ + r_in_tile;
-            const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(buf * kTileD);
-            float bias_row = 0.0f;
-            if (p.bias && p.transpose_out && rq < p.R_q) bias_row = __uint_as_float(uint32_t(p.bias[rq]) << 16);
+            const int64_t row = int64_t(ta) * kPairRows + int64_t(rank) * kTileRows + r_in_tile;
+            const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(buf * kPairRows);
 #pragma unroll 1
-            for (int c = 0; c < kTileD / 32; ++c) {
+            for (int c = 0; c < kPairRows / 32; ++c) {
+                const int64_t col0 = int64_t(tb) * kPairRows + c * 32;
+                if (col0 >= rows_b) break;   // warp-uniform: the rest of the tile is outside the output
                 uint32_t v[32];
                 tmem_ld32(taddr0 + uint32_t(c * 32), v);
                 tmem_ld_wait();
-                const int64_t rd0 = int64_t(td) * kTileD + c * 32;
-                if (p.transpose_out) {
-                    // out[r_d, r_q]: for a fixed register the 32 lanes write 32 consecutive r_q
-                    if (rq < p.R_q) {
+                if (row < rows_a) {
+                    uint16_t* dst = p.out + row * rows_b + col0;
+                    if (out_vec && col0 + 32 <= rows_b) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (rd0 + i < p.R_d) p.out[(rd0 + i) * p.R_q + rq] = f32_to_bf16_bits(__uint_as_float(v[i]) + bias_row);
-                    }
-                } else if (rq < p.R_q) {
-                    // out[r_q, r_d]: each lane owns 32 consecutive r_d of its row
-                    uint16_t* dst = p.out + rq * p.R_d + rd0;
-                    if (rd0 + 32 <= p.R_d && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                        uint32_t w[16];
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t w[8];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
-                            if (p.bias) {
-                                a += __uint_as_float(uint32_t(p.bias[rd0 + 2 * i]) << 16);
-                                b += __uint_as_float(uint32_t(p.bias[rd0 + 2 * i + 1]) << 16);
+                            for (int i = 0; i < 8; ++i) {
+                                float a = __uint_as_float(v[16 * h + 2 * i]), b = __uint_as_float(v[16 * h + 2 * i + 1]);
+                                if (p.bias) {
+                                    const uint32_t bb = __ldg(reinterpret_cast<const uint32_t*>(p.bias + col0) + 8 * h + i);
+                                    a += __uint_as_float(bb << 16);
+                                    b += __uint_as_float(bb & 0xFFFF0000u);
+                                }
+                                w[i] = pack_bf16(a, b);
                             }
-                            w[i] = uint32_t(f32_to_bf16_bits(a)) | (uint32_t(f32_to_bf16_bits(b)) << 16);
+                            st_global_v8(dst + 16 * h, w);
                         }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (rd0 + i < p.R_d) {
+                            if (col0 + i < rows_b) {
                                 float a = __uint_as_float(v[i]);
-                                if (p.bias) a += __uint_as_float(uint32_t(p.bias[rd0 + i]) << 16);
+                                if (p.bias) a += __uint_as_float(uint32_t(p.bias[col0 + i]) << 16);
                                 dst[i] = f32_to_bf16_bits(a);
                             }
                     }
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar(TEMPTY + buf));  // this accumulator may be overwritten
+            mbar_arrive_cluster(leader_bar(TEMPTY + buf));  // this accumulator may be overwritten
         }
     }
 
-    // common exit: normal completion or abort
+    // common exit: normal completion or abort.  Neither CTA leaves while the other may still arrive on its
+    // barriers or have its shared memory read by an MMA.
     tc_fence_before();
-    __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -541,9 +602,9 @@ __global__ void bounded_wait_selftest_kernel(long long budget_clocks) {
     const int warp = threadIdx.x >> 5;
     if ((threadIdx.x & 31) == 0) {
         if (warp == 0)
-            (void)mbar_wait(smem_u32(&bars[0]), 0, abort_flag, (9 << 8) | 0, budget_clocks);
+            (void)mbar_wait(smem_u32(&bars[0]), 0, abort_flag, 0u, (9 << 8) | 0, budget_clocks);
         else
-            (void)mbar_wait(smem_u32(&bars[1]), 0, abort_flag, (9 << 8) | 1);
+            (void)mbar_wait(smem_u32(&bars[1]), 0, abort_flag, 0u, (9 << 8) | 1);
     }
     __syncthreads();
 }
@@ -555,13 +616,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn fn = cached.load(std::memory_order_acquire);
     if (!fn) {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
+            qres == cudaDriverEntryPointSuccess) {
             fn = reinterpret_cast<EncodeTiledFn>(sym);
+            cached.store(fn, std::memory_order_release);
+        }
     }
     return fn;
 }
@@ -584,15 +648,16 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
         return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales, bias and out must be 2-byte aligned", who);
     if (R_d > (int64_t(1) << 31) - 1 || R_q > (int64_t(1) << 31) - 1 || K > (int64_t(1) << 31) - 1)
         return tcb::fail(TCB_ERR_TOO_LARGE, "%s: dimension beyond 2^31 - 1", who);
-    const int64_t tiles_q = (R_q + kTileQ - 1) / kTileQ, tiles_d = (R_d + kTileD - 1) / kTileD;
+    const int64_t tiles_q = (R_q + kPairRows - 1) / kPairRows, tiles_d = (R_d + kPairRows - 1) / kPairRows;
     if (tiles_q * tiles_d > (int64_t(1) << 30)) return tcb::fail(TCB_ERR_TOO_LARGE, "%s: too many output tiles", who);
 
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+    // dense operand: [R_d, K] bf16, one box = the 128 rows x 64 columns a CTA stages per K step
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(R_d)};
     const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileD)};
+    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileRows)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(dense), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -602,7 +667,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     CUtensorMap cmap;
     const cuuint64_t cdims[2] = {cuuint64_t(K), cuuint64_t(R_q)};
     const cuuint64_t cstrides[1] = {cuuint64_t(K)};
-    const cuuint32_t cbox[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileQ)};
+    const cuuint32_t cbox[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileRows)};
     cr = encode(&cmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(q), cdims, cstrides, cbox, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -615,13 +680,14 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
         {fused_dequant_gemm_kernel<5, false>, fused_dequant_gemm_kernel<5, true>},
         {fused_dequant_gemm_kernel<6, false>, fused_dequant_gemm_kernel<6, true>}};
     const int gi = group_size == 16 ? 0 : group_size == 32 ? 1 : 2;
-    const KernelFn kernel = kernels[gi][zp_or_null ? 1 : 0];
-    static bool attr_set[64][3][2] = {};
+    const int zi = zp_or_null ? 1 : 0;
+    const KernelFn kernel = kernels[gi][zi];
+    static std::atomic<bool> attr_set[64][3][2] = {};
     int dev = 0;
     TCB_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev][gi][zp_or_null ? 1 : 0]) {
+    if (dev < 0 || dev >= 64 || !attr_set[dev][gi][zi].load(std::memory_order_acquire)) {
         TCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-        attr_set[dev][gi][zp_or_null ? 1 : 0] = true;
+        if (dev >= 0 && dev < 64) attr_set[dev][gi][zi].store(true, std::memory_order_release);
     }
     Params p;
     p.q = q;
@@ -632,16 +698,15 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     p.R_q = R_q;
     p.R_d = R_d;
     p.K = K;
-    p.log2_g = group_size == 16 ? 4 : group_size == 32 ? 5 : 6;
     p.gpr = K / group_size;
-    p.chunk_vec_ok = p.gpr % 16 == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0 &&
+    p.table_vec_ok = p.gpr % 16 == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0 &&
                      (zp_or_null == nullptr || (reinterpret_cast<uintptr_t>(zp_or_null) & 15) == 0);
-    p.transpose_out = quant_is_rhs ? 1 : 0;
+    p.quant_is_a = quant_is_rhs ? 0 : 1;
     p.tiles_q = int(tiles_q);
     p.tiles_d = int(tiles_d);
     const int64_t num_tiles = tiles_q * tiles_d;
-    const int sms = tcb::sm_count();
-    const int grid = int(num_tiles < sms ? num_tiles : sms);
+    const int pairs = tcb::sm_count() / 2 > 0 ? tcb::sm_count() / 2 : 1;
+    const int grid = 2 * int(num_tiles < pairs ? num_tiles : pairs);   // a cluster of two CTAs per tile in flight
     kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
@@ -666,3 +731,4 @@ extern "C" int tcb_fused_dequant_linear_check(void* stream) {
     TCB_CUDA_TRY(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
     return tcb::fail(TCB_ERR_TIMEOUT, "tcb_fused_dequant_linear: a bounded wait ran out (role %d, barrier %d)", status >> 8, status & 0xff);
 }
+

@@ -14,9 +14,12 @@
 // hand that address to copies and kernels; this file does so once per device.
 #include "tcb_common.h"
 
+#include <atomic>
+
 namespace tcb {
 int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,
                       int group_size, cudaStream_t st);
+cudaError_t prime_amo_decompress();
 }
 
 namespace {
@@ -29,20 +32,27 @@ constexpr int64_t kScratchBytes = kOffZp + kMaxGroups;
 
 static __device__ __align__(256) uint8_t g_decode_staging[kScratchBytes];
 
-// Address of g_decode_staging on device `dev`, looked up on first use with that device current.
+// Address of g_decode_staging on the current device.  The first call on a device looks it up (which is also what
+// makes the runtime place the array and load this file's module there) and, in the same set-up step, makes every
+// decode kernel this entry point can choose resident, so that later calls neither load code nor query occupancy.
+// Two host threads making their first call at once both do the idempotent look-up; the cache word is atomic.
 cudaError_t staging_address(uint8_t** out) {
-    static uint8_t* cached[64] = {nullptr};
+    static std::atomic<uint8_t*> cached[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (!cached[dev]) {
+    uint8_t* base = cached[dev].load(std::memory_order_acquire);
+    if (!base) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_decode_staging);
         if (e != cudaSuccess) return e;
-        cached[dev] = static_cast<uint8_t*>(p);
+        e = tcb::prime_amo_decompress();
+        if (e != cudaSuccess) return e;
+        base = static_cast<uint8_t*>(p);
+        cached[dev].store(base, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = base;
     return cudaSuccess;
 }
 

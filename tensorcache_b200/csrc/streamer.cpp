@@ -27,6 +27,9 @@
 #if defined(__x86_64__)
 #include <immintrin.h>
 #endif
+#if defined(__linux__)
+#include <sys/mman.h>
+#endif
 
 namespace tcb {
 int launch_decompress(const uint8_t* q, const uint16_t* scales, const uint8_t* zp, uint16_t* out, int64_t numel,
@@ -162,6 +165,8 @@ void gather_rows(WorkerPool& pool, uint8_t* dst, int64_t row_bytes, int64_t n, c
     });
 }
 
+std::mutex g_shared_pool_call_mu;  // the shared pool runs one job at a time, whichever entry point asks
+
 WorkerPool& shared_pool(int want) {
     static std::mutex mu;
     static WorkerPool* pool = nullptr;
@@ -184,11 +189,45 @@ extern "C" int tcb_gather_rows(void* dst, const void* src_base, int64_t row_byte
     if (!dst || !src_base) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_gather_rows: null pointer");
     if (nthreads < 1) nthreads = 1;
     if (nthreads > 64) nthreads = 64;
-    static std::mutex call_mu;  // the shared pool runs one gather at a time
-    std::lock_guard<std::mutex> lk(call_mu);
+    std::lock_guard<std::mutex> lk(g_shared_pool_call_mu);
     const uint8_t* src = static_cast<const uint8_t*>(src_base);
     gather_rows(shared_pool(nthreads), static_cast<uint8_t*>(dst), row_bytes, n,
                 [&](int64_t i) { return src + (idx ? idx[i] : first_row + i) * row_bytes; });
+    return TCB_OK;
+}
+
+// Block copy into a freshly created, still sparse file mapping (the cache writer's output).  Every
+// 4 KB page of such a mapping is allocated and zero-filled by a page fault on first touch; taken one
+// by one inside the copy loop those faults, not the copy, set the writer's speed.  Each worker
+// therefore first asks the kernel to populate its slice in one call (MADV_POPULATE_WRITE, Linux 5.14+;
+// older kernels refuse it and the copy faults the pages as before), then streams its slice.
+extern "C" int tcb_write_block(void* dst, const void* src, int64_t bytes, int nthreads) {
+    if (bytes < 0) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_write_block: negative size");
+    if (bytes == 0) return TCB_OK;
+    if (!dst || !src) return tcb::fail(TCB_ERR_BAD_ARG, "tcb_write_block: null pointer");
+    if (nthreads < 1) nthreads = 1;
+    if (nthreads > 64) nthreads = 64;
+    constexpr int64_t kSlice = 2 << 20;   // slices start on 2 MB boundaries of the destination
+    uint8_t* d = static_cast<uint8_t*>(dst);
+    const uint8_t* s = static_cast<const uint8_t*>(src);
+    const uintptr_t d0 = reinterpret_cast<uintptr_t>(d);
+    const int64_t first = int64_t(d0 / kSlice), last = int64_t((d0 + uintptr_t(bytes) - 1) / kSlice);
+    const int64_t n_slices = last - first + 1;
+    std::lock_guard<std::mutex> lk(g_shared_pool_call_mu);
+    WorkerPool& pool = shared_pool(nthreads);
+    int parts = nthreads < n_slices ? nthreads : int(n_slices);
+    pool.run(parts, [&](int t) {
+        const int64_t s_lo = first + n_slices * t / parts, s_hi = first + n_slices * (t + 1) / parts;
+        uintptr_t lo = uintptr_t(s_lo) * kSlice, hi = uintptr_t(s_hi) * kSlice;
+        if (lo < d0) lo = d0;
+        if (hi > d0 + uintptr_t(bytes)) hi = d0 + uintptr_t(bytes);
+        if (hi <= lo) return;
+#if defined(__linux__)
+        const uintptr_t page = 4096, p_lo = (lo + page - 1) & ~(page - 1), p_hi = hi & ~(page - 1);
+        if (p_hi > p_lo) (void)madvise(reinterpret_cast<void*>(p_lo), p_hi - p_lo, 23 /* MADV_POPULATE_WRITE */);
+#endif
+        copy_row(reinterpret_cast<uint8_t*>(lo), s + (lo - d0), size_t(hi - lo));
+    });
     return TCB_OK;
 }
 
@@ -319,19 +358,45 @@ void producer_main(tcb_streamer* s) {
                 };
             };
             if (!s->d.direct_dma) {
-                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_q[slot]), qrow, rows, src(s->q_bases, qrow));
-                gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_s[slot]), srow, rows, src(s->s_bases, srow));
-                if (s->has_zp) gather_rows(*s->pool, static_cast<uint8_t*>(s->pinned_zp[slot]), zrow, rows, src(s->zp_bases, zrow));
+                // one pass over the batch's rows: each worker copies the codes, scales and zero points of its rows
+                int parts = s->pool->size();
+                if (parts > rows) parts = int(rows);
+                uint8_t* pq = static_cast<uint8_t*>(s->pinned_q[slot]);
+                uint8_t* ps = static_cast<uint8_t*>(s->pinned_s[slot]);
+                uint8_t* pz = s->has_zp ? static_cast<uint8_t*>(s->pinned_zp[slot]) : nullptr;
+                s->pool->run(parts, [&](int t) {
+                    const int64_t lo = rows * t / parts, hi = rows * (t + 1) / parts;
+                    for (int64_t i = lo; i < hi; ++i) {
+                        int sh;
+                        int64_t local;
+                        locate(s, idx ? idx[i] : first + i, sh, local);
+                        copy_row(pq + i * qrow, s->q_bases[sh] + local * qrow, size_t(qrow));
+                        copy_row(ps + i * srow, s->s_bases[sh] + local * srow, size_t(srow));
+                        if (pz) copy_row(pz + i * zrow, s->zp_bases[sh] + local * zrow, size_t(zrow));
+                    }
+                });
             }
             // the consumer's last read of this device slot (this pass or the one before)
             e = cudaStreamWaitEvent(s->copy_stream, s->released[slot], 0);
             if (e != cudaSuccess) { producer_fail(s, e, "cudaStreamWaitEvent(released)"); break; }
             if (!s->d.direct_dma) {
-                e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
-                if (e == cudaSuccess)
-                    e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
-                if (e == cudaSuccess && s->has_zp)
-                    e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+                // a full batch in a slot whose three arrays lie back to back (host and device alike) is one copy
+                const uint8_t *hq = static_cast<const uint8_t*>(s->pinned_q[slot]), *hs = static_cast<const uint8_t*>(s->pinned_s[slot]);
+                const uint8_t *dq = static_cast<const uint8_t*>(s->dev_q[slot]), *ds = static_cast<const uint8_t*>(s->dev_s[slot]);
+                bool one = hs == hq + rows * qrow && ds == dq + rows * qrow;
+                if (one && s->has_zp)
+                    one = static_cast<const uint8_t*>(s->pinned_zp[slot]) == hs + rows * srow &&
+                          static_cast<const uint8_t*>(s->dev_zp[slot]) == ds + rows * srow;
+                if (one) {
+                    e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * (qrow + srow + (s->has_zp ? zrow : 0))),
+                                        cudaMemcpyHostToDevice, s->copy_stream);
+                } else {
+                    e = cudaMemcpyAsync(s->dev_q[slot], s->pinned_q[slot], size_t(rows * qrow), cudaMemcpyHostToDevice, s->copy_stream);
+                    if (e == cudaSuccess)
+                        e = cudaMemcpyAsync(s->dev_s[slot], s->pinned_s[slot], size_t(rows * srow), cudaMemcpyHostToDevice, s->copy_stream);
+                    if (e == cudaSuccess && s->has_zp)
+                        e = cudaMemcpyAsync(s->dev_zp[slot], s->pinned_zp[slot], size_t(rows * zrow), cudaMemcpyHostToDevice, s->copy_stream);
+                }
             } else {
                 // The mapped shards are page-locked: the copy engine reads them directly.  Runs of
                 // consecutive rows of one shard become one copy.  Codes always go straight from the

@@ -22,7 +22,7 @@ import torch
 import ctypes
 
 from . import _lib
-from ._pipeline import NativePipeline, default_gather_threads, open_cache
+from ._pipeline import NativePipeline, open_cache, try_make_resident, writer_threads
 from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, dequantize_int8_g32
 
 
@@ -36,12 +36,20 @@ class FeatureCacheWriter:
     multiple of the group size (checked).
     """
 
-    _CHUNK = 64  # samples per encode launch, as the reference's CUDA path
+    _CHUNK = 256  # samples per encode launch (the reference's CUDA path takes 64; every sample is encoded on
+                  # its own, so the chunk size does not change a single code)
 
     def __init__(self, output_prefix: Union[str, Path], num_samples: int, seq_len: int, dim: int,
                  group_size: int = 32, adaptive: bool = False, amo_bq: bool = False, amo_lo: float = 0.95,
                  amo_hi: float = 1.05, amo_candidates: int = 32, amo_mode: Optional[str] = None,
                  num_shards: int = 1, quant_bits: int = 8, resume: bool = False):
+        self._resolve_settings(output_prefix, num_samples, seq_len, dim, group_size, adaptive, amo_bq, amo_lo, amo_hi,
+                               amo_candidates, amo_mode, num_shards, quant_bits, resume)
+        self._open_maps(resume)
+
+    def _resolve_settings(self, output_prefix, num_samples, seq_len, dim, group_size, adaptive, amo_bq, amo_lo, amo_hi,
+                          amo_candidates, amo_mode, num_shards, quant_bits, resume):
+        """Checks the settings and derives the file layout; touches no file."""
         self.output_prefix = Path(output_prefix)
         self.output_prefix.parent.mkdir(parents=True, exist_ok=True)
         if group_size <= 0:
@@ -82,6 +90,14 @@ class FeatureCacheWriter:
             self.shard_sizes = [num_samples]
             self.meta_path = str(self.output_prefix) + "_meta.json"
         self._shard_offsets = [int(v) for v in np.cumsum([0] + self.shard_sizes[:-1])]
+        self._member_of = None   # (manifest prefix, shard number) when this writer fills one shard of a sharded cache
+        self.current_idx = 0
+        self._closed = False
+        self._staging = None
+        self._maps = []
+
+    def _open_maps(self, resume: bool):
+        seq_len, dim, amo_bq = self.seq_len, self.dim, self.amo_bq
         mode = "r+" if resume else "w+"
         self._maps = []
         for pref, sz in zip(self.shard_prefixes, self.shard_sizes):
@@ -99,13 +115,53 @@ class FeatureCacheWriter:
                     np.memmap(paths[1], dtype=np.uint16, mode=mode, shape=(sz, self.scales_per_sample))]
             if amo_bq:
                 maps.append(np.memmap(paths[2], dtype=np.uint8, mode=mode, shape=(sz, self.scales_per_sample)))
+            for mm in maps:   # ask for huge pages where the file system offers them (fewer faults while filling the file)
+                try:
+                    mm._mmap.madvise(14)   # MADV_HUGEPAGE; refused harmlessly elsewhere
+                except (AttributeError, OSError, ValueError):
+                    pass
             self._maps.append(tuple(maps))
         self.int8_path = self.shard_prefixes[0] + "_int8.bin"
         self.scales_path = self.shard_prefixes[0] + "_scales.bin"
         self.zp_path = self.shard_prefixes[0] + "_zp.bin" if amo_bq else None
-        self.current_idx = 0
-        self._closed = False
-        self._staging = None
+
+    @classmethod
+    def for_shard(cls, output_prefix: Union[str, Path], shard_idx: int, num_samples: int, seq_len: int, dim: int,
+                  num_shards: int, **settings) -> "FeatureCacheWriter":
+        """Writer for ONE shard of a ``num_shards``-way cache of ``num_samples`` samples, so that several
+        processes (one per GPU) can fill a sharded cache together: shard ``i`` holds the global samples
+        ``[offset_i, offset_i + size_i)`` of the sequential split (feature_cache.py:134-142 of the reference) and
+        its writer takes exactly those, in order.  The files and the per-shard meta are byte-identical with what
+        ``FeatureCacheWriter(..., num_shards=num_shards)`` writes for that shard; one process calls
+        ``write_manifest`` with the same arguments to add ``<prefix>_shards.json``."""
+        num_shards = int(num_shards)
+        if not 0 <= shard_idx < num_shards:
+            raise ValueError(f"shard_idx {shard_idx} out of range {num_shards}")
+        if num_shards == 1:
+            return cls(output_prefix, num_samples, seq_len, dim, **settings)
+        base, rem = divmod(num_samples, num_shards)
+        obj = cls(f"{output_prefix}_shard{shard_idx}", base + (1 if shard_idx < rem else 0), seq_len, dim, **settings)
+        obj._member_of = (str(output_prefix), shard_idx)
+        return obj
+
+    @classmethod
+    def write_manifest(cls, output_prefix: Union[str, Path], num_samples: int, seq_len: int, dim: int, num_shards: int,
+                       **settings) -> str:
+        """Writes ``<prefix>_shards.json`` for a cache whose shards were filled by ``for_shard`` writers."""
+        obj = cls.__new__(cls)
+        kw = dict(group_size=32, adaptive=False, amo_bq=False, amo_lo=0.95, amo_hi=1.05, amo_candidates=32, amo_mode=None,
+                  quant_bits=8)
+        unknown = set(settings) - set(kw)
+        if unknown:
+            raise TypeError(f"unknown cache setting(s) {sorted(unknown)}")
+        kw.update(settings)
+        obj._resolve_settings(output_prefix, num_samples, seq_len, dim, kw["group_size"], kw["adaptive"], kw["amo_bq"],
+                              kw["amo_lo"], kw["amo_hi"], kw["amo_candidates"], kw["amo_mode"], num_shards, kw["quant_bits"], False)
+        obj._closed = True     # owns no file
+        if not obj.is_sharded:
+            raise ValueError("a manifest belongs to a cache of at least two shards")
+        obj._write_manifest(num_samples)
+        return obj.meta_path
 
     def __enter__(self):
         return self
@@ -187,16 +243,16 @@ class FeatureCacheWriter:
         event.synchronize()
         hq, hs, hz = self._host_staging(which)
         L = _lib.lib()
-        threads = default_gather_threads()
+        threads = writer_threads()
         pos = 0
         while pos < cur:
             si, li = self._shard_for_global(start + pos)
             li = int(li)
             take = int(min(cur - pos, self.shard_sizes[si] - li))
             for mm, host in zip(self._maps[si], (hq, hs, hz)):
-                row_bytes = int(mm[0].nbytes)
-                _lib.check(L.tcb_gather_rows(ctypes.c_void_p(mm[li:li + take].ctypes.data),
-                                             ctypes.c_void_p(int(host.data_ptr()) + int(pos) * row_bytes), row_bytes, None, 0, take, threads))
+                row_bytes = int(mm[0].nbytes)   # consecutive samples are contiguous in the file and in the landing buffer
+                _lib.check(L.tcb_write_block(ctypes.c_void_p(mm.ctypes.data + li * row_bytes),
+                                             ctypes.c_void_p(int(host.data_ptr()) + int(pos) * row_bytes), take * row_bytes, threads))
             pos += take
 
     def append(self, tensor_bf16: torch.Tensor):
@@ -258,22 +314,24 @@ class FeatureCacheWriter:
         self._maps = []
         self._staging = None
         if self.is_sharded:
-            metas = []
             for i, pref in enumerate(self.shard_prefixes):
                 actual = max(0, min(self.shard_sizes[i], self.current_idx - int(self._shard_offsets[i])))
                 with open(pref + "_meta.json", "w") as f:
                     json.dump(self._meta(actual, pref, with_bits=False), f, indent=2)
-                metas.append(pref + "_meta.json")
-            manifest = self._meta(self.current_idx, str(self.output_prefix), with_bits=False)
-            for k in ("int8_file", "scales_file", "zp_file"):
-                manifest.pop(k)
-            manifest.update(num_shards=self.num_shards, shard_sizes=self.shard_sizes, shard_prefixes=self.shard_prefixes,
-                            shard_metas=metas)
-            with open(self.meta_path, "w") as f:
-                json.dump(manifest, f, indent=2)
+            self._write_manifest(self.current_idx)
         else:
+            # one shard of a sharded cache carries the per-shard form of the meta (no "quant_bits" key)
             with open(self.meta_path, "w") as f:
-                json.dump(self._meta(self.current_idx, str(self.output_prefix), with_bits=True), f, indent=2)
+                json.dump(self._meta(self.current_idx, str(self.output_prefix), with_bits=self._member_of is None), f, indent=2)
+
+    def _write_manifest(self, total_written: int):
+        manifest = self._meta(total_written, str(self.output_prefix), with_bits=False)
+        for k in ("int8_file", "scales_file", "zp_file"):
+            manifest.pop(k)
+        manifest.update(num_shards=self.num_shards, shard_sizes=self.shard_sizes, shard_prefixes=self.shard_prefixes,
+                        shard_metas=[pref + "_meta.json" for pref in self.shard_prefixes])
+        with open(self.meta_path, "w") as f:
+            json.dump(manifest, f, indent=2)
 
 
 class FeatureCacheDataset(torch.utils.data.Dataset):
@@ -289,9 +347,11 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
 
     def __init__(self, cache_prefix: Union[str, Path], auto_dequant_device: Optional[str] = None,
                  shard_idx: Optional[int] = None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 all_rank_shards: bool = False):
+                 all_rank_shards: bool = False, pin_shard: Optional[bool] = None):
         self.cache_prefix = Path(cache_prefix)
-        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards)
+        self._pin_wanted = pin_shard     # as for ZeroCopyTensorStreamer: True / False / None (automatic, decided at the
+        self.pin_shard = False           # first iter_batches call); copy-on-write mappings can be page-locked later
+        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards, private=pin_shard is not False)
         lay = self._layout
         self.meta = lay.meta
         self.is_sharded = lay.selected is not None
@@ -304,6 +364,8 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
         self.scales_count = lay.groups_per_sample
         self.auto_dequant_device = auto_dequant_device
         self._pipes = []
+        self._idle_pipes = {}
+        self._closed = False
 
     def __len__(self) -> int:
         return self.num_samples
@@ -330,9 +392,20 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
         """Yields bf16 ``[rows, seq_len, dim]`` views of a two-slot output ring
         (valid until two more batches have been requested), or cloned
         ``(q, scales, zp)`` device tensors (``(q, scales)`` for a symmetric cache) when
-        ``dequantize=False``."""
-        pipe = NativePipeline(self._layout, batch_size, torch.device(device), n_slots=2)
+        ``dequantize=False``.
+
+        The first call decides the reader mode (``pin_shard`` of the constructor): with the shard(s)
+        page-locked in host memory the rows go to the GPU without a CPU copy, exactly as in
+        ``ZeroCopyTensorStreamer``; the page-locking is paid once and kept until ``close()``.  The ring of
+        a pass is kept for the next pass with the same batch size and device."""
+        dev = torch.device(device)
+        self.pin_shard = try_make_resident(self._layout, dev, self._pin_wanted)
+        key = (int(batch_size), str(dev), self.pin_shard)
+        pipe = self._idle_pipes.pop(key, None)
+        if pipe is None:
+            pipe = NativePipeline(self._layout, batch_size, dev, n_slots=2, pin_shards=self.pin_shard)
         self._pipes.append(pipe)
+        finished = False
         try:
             if shuffle:
                 order = np.arange(self.num_samples)
@@ -355,15 +428,21 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
                         out += (pipe.dev_zp[slot][:rows].clone(),)
                     pipe.release()
                     yield out
+            finished = True
         finally:
             torch.cuda.synchronize(pipe.device)
-            pipe.close()
             self._pipes.remove(pipe)
+            if finished and key not in self._idle_pipes and not self._closed:
+                self._idle_pipes[key] = pipe      # reused by the next pass
+            else:
+                pipe.close()
 
     def close(self):
-        for p in list(getattr(self, "_pipes", [])):
+        self._closed = True
+        for p in list(getattr(self, "_pipes", [])) + list(getattr(self, "_idle_pipes", {}).values()):
             p.close()
         self._pipes = []
+        self._idle_pipes = {}
         if getattr(self, "_layout", None) is not None:
             self._layout.close()
 

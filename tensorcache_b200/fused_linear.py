@@ -9,8 +9,9 @@ along the last dimension) and a dense bf16 ``weight``.  On top of that:
 * ``fused_dequant_matmul(x, wq, ws, wzp)`` is the quantised-*weight* form
   ``x @ dequant(W).T`` used when the weight matrix is what sits in the cache.
 
-Both run the same kernel; the second writes its output transposed.  The inner
-dimension must be a multiple of the group size.
+Both run the same kernel: the operand whose rows are the output's rows becomes the
+M side of the tensor-core tile, so either form stores row-contiguous vectors.  The
+inner dimension must be a multiple of the group size.
 """
 from __future__ import annotations
 

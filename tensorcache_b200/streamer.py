@@ -14,11 +14,13 @@ Differences from the reference, on purpose:
   (manifest, rank -> shard mapping, ``len``) work without a GPU;
 * ``all_rank_shards=True`` lets a rank read every shard ``i`` with
   ``i % world_size == rank`` instead of the single shard ``rank % num_shards``;
-* ``pin_shard=True`` keeps the opened shard(s) resident and page-locked in host memory
-  (a private mapping of the files, pinned once at about 0.4 s per GB, costing as much RAM
-  as the shard) so that the copy engine reads the rows itself and no CPU copy remains;
-  the default ``False`` keeps the reference's small-footprint behaviour (rows are copied
-  into page-locked staging by worker threads);
+* ``pin_shard`` chooses how rows reach the GPU.  ``True`` keeps the opened shard(s) resident and
+  page-locked in host memory (a private mapping of the files, pinned once at about 0.4 s per GB,
+  costing as much RAM as the shard) so that the copy engine reads the rows itself and no CPU copy
+  remains.  ``False`` is the reference's small-footprint behaviour (worker threads copy rows into
+  page-locked staging).  The default ``None`` picks the first when the shard(s) fit a quarter of the
+  host memory available at that moment and the driver agrees to page-lock them, and the second,
+  with a one-line warning, otherwise;
 * the ring has three slots by default (``ring_slots``; the reference has two), which
   costs one more batch of staging and output memory and hides the host gather.
 """
@@ -30,7 +32,7 @@ from typing import Iterator, Optional, Union
 import numpy as np
 import torch
 
-from ._pipeline import NativePipeline, open_cache
+from ._pipeline import NativePipeline, open_cache, try_make_resident
 
 
 class ZeroCopyTensorStreamer:
@@ -47,7 +49,7 @@ class ZeroCopyTensorStreamer:
         all_rank_shards: bool = False,
         gather_threads: Optional[int] = None,
         ring_slots: Optional[int] = None,
-        pin_shard: bool = False,
+        pin_shard: Optional[bool] = None,
     ):
         self.cache_prefix = Path(cache_prefix)
         self.batch_size = int(batch_size)
@@ -56,8 +58,9 @@ class ZeroCopyTensorStreamer:
         self.low_vram = low_vram
         self.rank = rank
         self.world_size = world_size
-        self.pin_shard = bool(pin_shard)
-        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards, private=self.pin_shard)
+        self._pin_wanted = pin_shard            # True / False / None (automatic)
+        self.pin_shard = False                  # what the reader ended up doing; set when the pipeline is built
+        self._layout = open_cache(cache_prefix, shard_idx, rank, world_size, all_rank_shards, private=pin_shard is not False)
         lay = self._layout
         self.meta = lay.meta
         self.is_sharded = lay.selected is not None and len(lay.shards) > 1
@@ -108,6 +111,7 @@ class ZeroCopyTensorStreamer:
         if self._closed:
             raise RuntimeError("streamer is closed")
         if self._pipe is None:
+            self.pin_shard = try_make_resident(self._layout, self.device, self._pin_wanted)
             self._pipe = NativePipeline(self._layout, self.batch_size, self.device, self.n_bufs, self._gather_threads,
                                         pin_shards=self.pin_shard)
             self.out_bf16 = self._pipe.dev_out

@@ -100,3 +100,24 @@ def auto_select_mode(x: torch.Tensor, target_rmse: float = 0.5, group_size: int 
     if group_size > 16:
         return f"G16_{auto_select_mode(x, target_rmse, 16, include_quality)}"
     return "quality" if include_quality else "max"
+
+
+def selftest_sum_order(rows_per_group_size: int = 4000, seed: int = 9) -> None:
+    """Checks on THIS host that ``torch.sum(dim=-1)`` over a group's fp32 terms (what the reference's scale
+    search compares, src/tensorcache/codec.py:877) adds in the order the encode kernels assume.  The order
+    belongs to the torch build and the CPU's vector ISA; if it differs here, encoded scales can differ from
+    what this host's own reference run would produce, and the call raises ``RuntimeError`` saying so.  Needs
+    no GPU."""
+    import ctypes
+
+    from . import _lib
+
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(seed)
+    for G in (8, 16, 24, 32, 48, 64, 128):
+        e = (torch.rand(rows_per_group_size, G, generator=g) * torch.exp(4 * torch.randn(rows_per_group_size, 1, generator=g))).contiguous()
+        sums = e.sum(dim=-1).contiguous()
+        rc = L.tcb_selftest_sum_order(ctypes.c_void_p(e.data_ptr()), rows_per_group_size, G, ctypes.c_void_p(sums.data_ptr()))
+        if rc == _lib.ERR_SUM_ORDER:
+            raise RuntimeError(L.tcb_last_error().decode("utf-8", "replace"))
+        _lib.check(rc)

@@ -98,3 +98,27 @@ def test_product_package_does_not_touch_the_oracle():
         text = p.read_text()
         assert "oracle" not in text.replace("oracle/", ""), f"{p} mentions the oracle"
         assert "import triton" not in text and "torch.compile" not in text
+
+
+def test_sum_order_selftest_passes_here_and_detects_another_order(built_lib):
+    """tcb_selftest_sum_order (host only): this host's torch.sum(dim=-1) matches the order the encoders use,
+    and a sum taken in plain left-to-right order is reported with its own status."""
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    import tensorcache_b200 as tc
+    from tensorcache_b200 import _lib
+
+    tc.selftest_sum_order(rows_per_group_size=500)
+    g = torch.Generator().manual_seed(1)
+    e = (torch.rand(2000, 32, generator=g) * torch.exp(4 * torch.randn(2000, 1, generator=g))).contiguous()
+    seq = np.zeros(2000, np.float32)
+    for k in range(32):                       # strict left-to-right accumulation: another order
+        seq = (seq + e[:, k].numpy()).astype(np.float32)
+    assert not np.array_equal(seq.view(np.uint32), e.sum(-1).numpy().view(np.uint32))
+    rc = built_lib.tcb_selftest_sum_order(ctypes.c_void_p(e.data_ptr()), 2000, 32, seq.ctypes.data)
+    assert rc == _lib.ERR_SUM_ORDER and b"order" in built_lib.tcb_last_error()
+    assert built_lib.tcb_selftest_sum_order(None, 0, 32, None) == 0
+    assert built_lib.tcb_selftest_sum_order(ctypes.c_void_p(e.data_ptr()), 10, 20, seq.ctypes.data) == _lib.ERR_GROUP_SIZE

@@ -185,7 +185,7 @@ def test_symmetric_writer_output_is_byte_identical_with_the_reference_writer(tmp
 def test_readers_on_reference_written_symmetric_caches(golden_sym_rows, sub):
     want = np.concatenate([golden_sym_rows[f"{sub}/{i}/rec"] for i in range(7)])
     prefix = GOLDEN / sub / "feat"
-    for kw in (dict(), dict(low_vram=True), dict(pin_shard=True)):
+    for kw in (dict(), dict(pin_shard=False), dict(low_vram=True), dict(pin_shard=True)):
         with tc.ZeroCopyTensorStreamer(prefix, batch_size=2, device=DEV, shuffle=False, **kw) as st:
             assert not st.amo_bq
             for _ in range(2):
@@ -232,9 +232,9 @@ def test_benchmark_shape_cache_round_trip(tmp_path):
     w.append(x[:200].to(DEV)); w.append(x[200:]); w.close()
     q, s, zp, _ = tc.compress(x.to(DEV), "balanced", 32)
     want = tc.decompress(q, s, (320, 446, 768), zp, 32)
-    for kw in (dict(), dict(pin_shard=True)):
+    for kw in (dict(), dict(pin_shard=False), dict(pin_shard=True)):
         with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=128, device=DEV, shuffle=False, **kw) as st:
-            assert len(st) == 3
+            assert len(st) == 3 and st.pin_shard == kw.get("pin_shard", True)   # automatic mode: resident, the shards are small
             got = torch.cat([b.clone() for b in st])
             assert torch.equal(got.view(torch.int16), want.view(torch.int16)), kw
             st.shuffle = True
@@ -246,3 +246,77 @@ def test_benchmark_shape_cache_round_trip(tmp_path):
         with tc.FeatureCacheDataset(tmp_path / "feat", rank=r, world_size=2) as ds:
             got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=128, shuffle=False, device=DEV)])
             assert torch.equal(got.view(torch.int16), want[160 * r:160 * (r + 1)].view(torch.int16))
+
+
+def test_automatic_reader_mode_and_its_fallback(tmp_path, monkeypatch):
+    """pin_shard=None (the default) page-locks the shard when it fits the memory budget and otherwise reads through
+    staging copies with a warning; both return the same bits.  FeatureCacheDataset.iter_batches follows the same
+    rule, pays the page-locking once, and reuses its ring for the next pass."""
+    from tensorcache_b200 import _pipeline
+
+    x = synth.config0_style(43, (150, 32, 256))
+    w = tc.FeatureCacheWriter(tmp_path / "feat", 150, 32, 256, group_size=32, amo_bq=True, amo_mode="fast")
+    w.append(x.to(DEV)); w.close()
+    q, s, zp, _ = tc.compress(x.to(DEV), "fast", 32)
+    want = bits(tc.decompress(q, s, (150, 32, 256), zp, 32)).reshape(150, -1)
+    with tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False) as st:
+        assert st.pin_shard is True
+        assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(150, -1), want)
+    with tc.FeatureCacheDataset(tmp_path / "feat") as ds:
+        for _ in range(2):
+            got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=64, shuffle=False, device=DEV)])
+            assert ds.pin_shard is True and np.array_equal(bits(got).reshape(150, -1), want)
+        assert len(ds._idle_pipes) == 1 and not ds._pipes          # one ring, kept between the passes
+        it = ds.iter_batches(batch_size=64, shuffle=False, device=DEV)
+        first = next(it).clone()
+        it.close()                                                  # an abandoned pass gives its ring back
+        assert np.array_equal(bits(first).reshape(64, -1), want[:64]) and not ds._pipes
+        np.random.seed(3)
+        raw = list(ds.iter_batches(batch_size=50, shuffle=False, device=DEV, dequantize=False))
+        assert len(raw) == 3 and torch.equal(torch.cat([r[0] for r in raw]).view(-1), q)
+    monkeypatch.setattr(_pipeline, "MEM_FRACTION_FOR_RESIDENT_SHARDS", 0.0)
+    with pytest.warns(UserWarning, match="staging"):
+        st = tc.ZeroCopyTensorStreamer(tmp_path / "feat", batch_size=64, device=DEV, shuffle=False)
+    with st:
+        assert st.pin_shard is False
+        assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(150, -1), want)
+    with pytest.raises(Exception):   # an explicit request is not silently downgraded: a read-only mapping cannot be page-locked
+        lay = _pipeline.open_cache(tmp_path / "feat", private=False)
+        try:
+            _pipeline.try_make_resident(lay, torch.device(DEV), True)
+        finally:
+            lay.close()
+
+
+def test_per_shard_writers_fill_the_same_cache_as_one_sharded_writer(tmp_path):
+    """FeatureCacheWriter.for_shard + write_manifest (one process per shard) against FeatureCacheWriter(num_shards=3):
+    every file byte-identical, manifests equal up to the path strings, and the readers take it by rank / world_size."""
+    x = synth.config0_style(44, (100, 16, 128))
+    kw = dict(group_size=16, amo_bq=True, amo_mode="balanced")
+    one = tc.FeatureCacheWriter(tmp_path / "a" / "feat", 100, 16, 128, num_shards=3, **kw)
+    one.append(x.to(DEV)); one.close()
+    sizes, off = [34, 33, 33], 0
+    for i, n in enumerate(sizes):
+        w = tc.FeatureCacheWriter.for_shard(tmp_path / "b" / "feat", i, 100, 16, 128, 3, **kw)
+        assert w.num_samples == n
+        w.append(x[off:off + n].to(DEV)); w.close()
+        off += n
+    tc.FeatureCacheWriter.write_manifest(tmp_path / "b" / "feat", 100, 16, 128, 3, **kw)
+    names = sorted(f.name for f in (tmp_path / "a").iterdir())
+    assert names == sorted(f.name for f in (tmp_path / "b").iterdir()) and len(names) == 3 * 4 + 1
+    for name in names:
+        fa, fb = tmp_path / "a" / name, tmp_path / "b" / name
+        if name.endswith(".bin"):
+            assert fa.read_bytes() == fb.read_bytes(), name
+        else:
+            a, b = json.loads(fa.read_text()), json.loads(fb.read_text())
+            for k in ("shard_prefixes", "shard_metas"):
+                a.pop(k, None), b.pop(k, None)
+            assert a == b, name
+    q, s, zp, _ = tc.compress(x.to(DEV), "balanced", 16)
+    want = bits(tc.decompress(q, s, (100, 16, 128), zp, 16)).reshape(100, -1)
+    with tc.ZeroCopyTensorStreamer(tmp_path / "b" / "feat", batch_size=32, device=DEV, shuffle=False, rank=1, world_size=3) as st:
+        assert st.num_samples == 33
+        assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(33, -1), want[34:67])
+    with pytest.raises(ValueError):
+        tc.FeatureCacheWriter.for_shard(tmp_path / "c" / "feat", 3, 100, 16, 128, 3, **kw)
