@@ -405,7 +405,7 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
         if pipe is None:
             pipe = NativePipeline(self._layout, batch_size, dev, n_slots=2, pin_shards=self.pin_shard)
         self._pipes.append(pipe)
-        finished = False
+        reusable = False
         try:
             if shuffle:
                 order = np.arange(self.num_samples)
@@ -428,11 +428,14 @@ class FeatureCacheDataset(torch.utils.data.Dataset):
                         out += (pipe.dev_zp[slot][:rows].clone(),)
                     pipe.release()
                     yield out
-            finished = True
+            reusable = True
+        except GeneratorExit:
+            reusable = True       # an abandoned pass: no batch is held at a yield, and the next begin() drops what is in flight
+            raise
         finally:
             torch.cuda.synchronize(pipe.device)
             self._pipes.remove(pipe)
-            if finished and key not in self._idle_pipes and not self._closed:
+            if reusable and key not in self._idle_pipes and not self._closed:
                 self._idle_pipes[key] = pipe      # reused by the next pass
             else:
                 pipe.close()

@@ -31,7 +31,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
 
 
+def _aligned(t: Optional[torch.Tensor], nbytes: int = 16) -> Optional[torch.Tensor]:
+    """The TMA descriptors need 16-byte aligned operands.  A contiguous view into a larger tensor (``w[1:]``,
+    ``q[3:]``) can start anywhere, so such an operand is copied once; aligned tensors pass through untouched."""
+    if t is None or t.data_ptr() % nbytes == 0:
+        return t
+    return t.clone(memory_format=torch.contiguous_format)
+
+
 def _launch(dense, q, scales, zp, bias, out, R_d, R_q, K, group_size, quant_is_rhs):
+    dense, q = _aligned(dense), _aligned(q)
     dev = dense.device
     with torch.cuda.device(dev):
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)

@@ -99,6 +99,31 @@ def test_dequantised_operand_equals_the_decode_kernel_bits():
     assert torch.equal(y.t().contiguous().view(torch.int16), want.view(torch.int16))
 
 
+def test_operands_that_are_views_at_odd_offsets():
+    """Slices of larger tensors are contiguous but need not start on a 16-byte boundary (the reference's Triton
+    kernel takes them as they are); the wrapper realigns them instead of refusing."""
+    M, N, K, G = 96, 160, 256, 32
+    g = torch.Generator().manual_seed(5)
+    xb = torch.randn(M + 1, K, generator=g).to(torch.bfloat16).to(DEV)
+    x = xb.view(-1)[3:3 + M * K].view(M, K)                       # starts 6 bytes into the allocation
+    w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16).to(DEV)
+    wq, ws, wzp, _ = tc.compress(w, "balanced", G)
+    qb = torch.zeros(N * K + 16, dtype=torch.uint8, device=DEV)
+    qb[5:5 + N * K] = wq
+    wq_view = qb[5:5 + N * K].view(N, K)                           # starts 5 bytes into the allocation
+    assert x.data_ptr() % 16 != 0 and wq_view.data_ptr() % 16 != 0 and x.is_contiguous() and wq_view.is_contiguous()
+    y = tc.fused_dequant_matmul(x, wq_view, ws, wzp, None, G)
+    check_device_status()
+    ref = x.float() @ dequant_f32(wq.view(N, K), ws, wzp, G).T
+    assert rel_fro(y, ref) <= EXPECTED
+    layer = tc.FusedDequantLinear(K, M, bias=False, group_size=G).to(DEV)
+    with torch.no_grad():
+        layer.weight.copy_(x)
+    y2 = layer(wq_view, ws, wzp)                                    # [N, M] = deq(W) @ x^T
+    check_device_status()
+    assert rel_fro(y2, ref.T) <= EXPECTED
+
+
 def test_argument_errors():
     x = torch.zeros(8, 96, dtype=torch.bfloat16, device=DEV)
     wq = torch.zeros(8, 96, dtype=torch.uint8, device=DEV)

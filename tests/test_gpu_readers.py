@@ -269,8 +269,10 @@ def test_automatic_reader_mode_and_its_fallback(tmp_path, monkeypatch):
         assert len(ds._idle_pipes) == 1 and not ds._pipes          # one ring, kept between the passes
         it = ds.iter_batches(batch_size=64, shuffle=False, device=DEV)
         first = next(it).clone()
-        it.close()                                                  # an abandoned pass gives its ring back
-        assert np.array_equal(bits(first).reshape(64, -1), want[:64]) and not ds._pipes
+        it.close()                                                  # an abandoned pass gives its ring back for reuse
+        assert np.array_equal(bits(first).reshape(64, -1), want[:64]) and not ds._pipes and len(ds._idle_pipes) == 1
+        got = torch.cat([b.clone() for b in ds.iter_batches(batch_size=64, shuffle=False, device=DEV)])
+        assert np.array_equal(bits(got).reshape(150, -1), want)    # and the next pass starts from the beginning
         np.random.seed(3)
         raw = list(ds.iter_batches(batch_size=50, shuffle=False, device=DEV, dequantize=False))
         assert len(raw) == 3 and torch.equal(torch.cat([r[0] for r in raw]).view(-1), q)

@@ -186,3 +186,25 @@ def test_two_ranks_cover_a_three_shard_cache_exactly_once(golden_rows):
     want = {i: int(golden_rows[f"cache_sharded/{i}/q"].astype(np.int64).sum()) for i in range(7)}
     assert sums[0] == [want[0], want[1], want[2], want[5], want[6]]
     assert sums[1] == [want[3], want[4]]
+
+
+def test_manifest_written_for_per_shard_writers_equals_the_reference_manifest(tmp_path):
+    """FeatureCacheWriter.write_manifest (the piece one rank adds when every rank filled its own shard) produces the
+    manifest the reference's sharded writer wrote for the same cache, path strings aside.  Needs no GPU."""
+    import json
+
+    import tensorcache_b200 as tc
+
+    ref = json.loads((GOLDEN / "cache_sharded" / "feat_shards.json").read_text())
+    path = tc.FeatureCacheWriter.write_manifest(tmp_path / "feat", ref["num_samples"], ref["seq_len"], ref["dim"], ref["num_shards"],
+                                                group_size=ref["group_size"], amo_bq=True, amo_mode=ref["amo_mode"])
+    mine = json.loads(open(path).read())
+    assert [os.path.basename(p) for p in mine["shard_prefixes"]] == [f"feat_shard{i}" for i in range(ref["num_shards"])]
+    for k in ("shard_prefixes", "shard_metas"):
+        mine.pop(k), ref.pop(k)
+    assert mine == ref
+    assert not list(tmp_path.glob("*.bin"))          # touches no data file
+    with pytest.raises(ValueError):
+        tc.FeatureCacheWriter.write_manifest(tmp_path / "single", 7, 6, 64, 1)
+    with pytest.raises(TypeError):
+        tc.FeatureCacheWriter.write_manifest(tmp_path / "bad", 7, 6, 64, 3, colour="red")

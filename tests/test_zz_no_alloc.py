@@ -1,5 +1,5 @@
 """The allocation-free decode entry point (host codes -> device bf16 through the library's
-built-in staging array) against the regular entry point, through the C ABI.
+built-in staging array) against the regular entry point and the CPU oracle, through the C ABI.
 
 This file is named so that pytest collects it last: if it fails under ``-x`` every other
 test has already run.  It also passes when run alone in a fresh process."""
@@ -33,6 +33,7 @@ def _noalloc(L, dev, q, s, zp, G):
 
 
 def test_noalloc_decode_matches_regular_entry_point_on_consecutive_calls(built_lib):
+    from oracle import amo_oracle as orc
     from tensorcache_b200 import _lib
 
     L = built_lib
@@ -51,6 +52,20 @@ def test_noalloc_decode_matches_regular_entry_point_on_consecutive_calls(built_l
         assert np.array_equal(got, want), (numel, G)          # bit-exact, as every decode test
         got2 = _noalloc(L, dev, q, s, zp, G)                  # same call again
         assert np.array_equal(got2, want), (numel, G)
+        assert np.array_equal(got.view(np.uint16), orc.decompress(q, s, zp, G)), (numel, G)   # and directly against the CPU oracle
+    # a call after the set-up call takes no device memory: the free-memory figure of the driver does not move
+    numel, G = 1 << 20, 32
+    q = rng.integers(0, 256, numel, dtype=np.uint8)
+    zp = rng.integers(0, 256, numel // G, dtype=np.uint8)
+    s = np.full(numel // G, 0x3C00, np.uint16)
+    out = torch.empty(numel, dtype=torch.int16, device=dev)
+    st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    torch.cuda.synchronize(dev)
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    for _ in range(3):
+        assert L.tcb_decompress_amo_host_noalloc(q.ctypes.data, s.ctypes.data, zp.ctypes.data, out.data_ptr(), numel, G, st) == 0
+    torch.cuda.synchronize(dev)
+    assert torch.cuda.mem_get_info(dev)[0] == free_before
     # sizes beyond the built-in staging area are refused before anything is enqueued
     big = np.zeros(8, np.uint8)
     rc = L.tcb_decompress_amo_host_noalloc(big.ctypes.data, big.ctypes.data, big.ctypes.data, 16, _lib.NOALLOC_MAX_VALUES + 1, 32, None)
