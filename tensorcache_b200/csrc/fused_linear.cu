@@ -9,15 +9,23 @@
 // UMMA operand layout).  The dense operand arrives by TMA into the same layout.
 //
 // The kernel runs as pairs of CTAs (a cluster of two, one CTA per SM of a TPC) that
-// issue tcgen05.mma.cta_group::2: one 256 x 256 output tile per pair, K advancing 64
-// at a time through a 5-stage ring.  Each CTA of the pair dequantises 128 rows of the
-// quantised operand and loads 128 rows of the dense one; the tensor cores of the two
-// SMs exchange the halves of the N-side operand between themselves, so per flop each
-// SM moves a third fewer operand bytes through its shared memory than a single-CTA
-// 128 x 256 tile does.  That matters because the shared-memory data pipe (one 128-byte
-// wavefront per clock), not the tensor pipe, is what bounds this kernel: per K step it
-// serves the tensor core's operand reads (256 wavefronts), the TMA's writes (192) and
-// the producers' loads and stores (about 270), against the 512 clocks the step's MMAs take.
+// issue tcgen05.mma.cta_group::2.  A pair owns an output tile of 256 rows of the
+// quantised operand x 512 rows of the dense one; K advances 64 at a time through a
+// 3-stage ring.  Each CTA dequantises 128 rows of q and loads 256 dense rows per stage;
+// per K step the leader issues two groups of four MMAs (M 256, N 256, K 16), one group
+// per half of the CTAs' dense rows, into the two 256-column accumulators that fill
+// the 512 TMEM columns.
+//
+// Why this shape.  What bounds a kernel of this kind is the shared-memory data pipe of
+// the SM (one 128-byte wavefront per clock): it serves the tensor core's operand reads,
+// the TMA's writes and the producers' loads and stores.  A single-CTA 128 x 256 tile
+// needs about 1150 wavefronts per 512 clocks of MMA work, a pair on a 256 x 256 tile
+// 730 (the tensor cores of the two SMs exchange the halves of the N-side operand, so
+// each CTA stages half of it), and this tile 1110 per 1024 clocks: every dequantised
+// tile, the expensive one to make, is used against twice as many dense rows.  The price
+// is that both accumulators belong to one tile, so the epilogue no longer overlaps the
+// next tile's MMAs; the eight epilogue warps hand the accumulators back as soon as they
+// have read them.
 //
 // Which operand is the M side depends on the wanted output layout, so that every
 // epilogue store is a row-contiguous vector store:
@@ -27,24 +35,23 @@
 //
 // Warp roles, per CTA:
 //   warp 0      TMA producer (one thread): raw code tile [128 x 64] uint8 into the CTA's
-//               own barrier, dense tile [128 x 64] bf16 (128-byte swizzle) into the
+//               own barrier, dense tile [256 x 64] bf16 (128-byte swizzle) into the
 //               leader CTA's barrier (cp.async.bulk.tensor with cta_group::2, no multicast)
-//   warp 1      leader CTA only, one thread: per stage ONE barrier wait (dense halves of both
-//               CTAs landed + all 16 producer warps of the pair done), 4 x tcgen05.mma
-//               (M256 N256 K16) and ONE tcgen05.commit that arrives on the stage barrier of
-//               both CTAs; after the last K step one more on both accumulator barriers.
-//               This thread's serial latency per stage is on the critical path, hence the
-//               merged barrier and the single commit.  In both CTAs this warp owns the
-//               TMEM allocation.
+//   warp 1      leader CTA only, one thread: per stage ONE barrier wait (dense rows of both
+//               CTAs landed + all 16 producer warps of the pair done), 8 x tcgen05.mma and
+//               ONE tcgen05.commit that arrives on the stage barrier of both CTAs; after the
+//               last K step one more on both accumulator barriers.  This thread's serial
+//               latency per stage is on the critical path, hence the merged barrier and the
+//               single commit.  In both CTAs this warp owns the TMEM allocation.
 //   warps 2-9   dequantising producers: 16 rows per warp.  A warp instruction reads 512
 //               contiguous bytes of codes and writes 16-byte pieces that cover all 32
 //               banks per quarter warp, so neither side has bank conflicts.  Scales and
 //               zero points sit merged (scale << 16 | zp) in a per-warp shared-memory
 //               table of 32 groups per row that the warp refills itself one table ahead
 //               (global -> registers -> table), so a turn-over needs only a warp sync.
-//   warps 10-13 epilogue: tcgen05.ld -> (+bias) -> bf16 -> global (32-byte stores)
-// The 512 TMEM columns hold two 256-column fp32 accumulators, so the epilogue of
-// one tile overlaps the main loop of the next.  No TMA multicast anywhere.
+//   warps 10-17 epilogue, one per TMEM lane quadrant and accumulator:
+//               tcgen05.ld -> (+bias) -> bf16 -> global (32-byte stores)
+// No TMA multicast anywhere.
 //
 // The dequantised value is bf16((q - zp) * scale), the number the decode kernel produces:
 // the code byte is spliced into the mantissa of 2^15, one FMA with the exact constant
@@ -68,14 +75,16 @@ namespace {
 constexpr int kTileRows = 128;   // rows of each operand per CTA and tile
 constexpr int kPairRows = 256;   // rows of each operand per CTA pair and tile (MMA M = N = 256)
 constexpr int kBlockK = 64;      // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kStages = 5;
+constexpr int kStages = 3;
+constexpr int kDenseRows = 256;  // dense rows per CTA and tile: two MMA groups of 128
+constexpr int kPairDense = 512;  // dense rows per CTA pair and tile
 constexpr int kNumProducerWarps = 8;
-constexpr int kNumEpilogueWarps = 4;
-constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 448
+constexpr int kNumEpilogueWarps = 8;
+constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 576
 constexpr int kFirstProducerWarp = 2;
 constexpr int kFirstEpilogueWarp = 2 + kNumProducerWarps;                   // 10
 constexpr uint32_t kStageBytesQ = kTileRows * kBlockK * 2;                   // 16 KB dequantised operand
-constexpr uint32_t kStageBytesD = kTileRows * kBlockK * 2;                   // 16 KB dense operand
+constexpr uint32_t kStageBytesD = kDenseRows * kBlockK * 2;                  // 32 KB dense operand
 constexpr uint32_t kStageBytesC = kTileRows * kBlockK;                       // 8 KB of raw codes
 constexpr int kTableGroups = 32;                                             // groups per row in the scale table
 constexpr uint32_t kTableRowBytes = kTableGroups * 4 + 16;                   // 144: the pad spreads 8 rows over all banks
@@ -359,7 +368,7 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
     auto bar = [&](int id) { return bar0 + 8u * uint32_t(id); };
     auto leader_bar = [&](int id) { return map_to_cta(bar(id), 0); };
     const uint32_t abort_peer = map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1);
-    const int FULL = 0, EMPTY = kStages, FULL_C = 2 * kStages, TFULL = 3 * kStages, TEMPTY = 3 * kStages + 2;
+    const int FULL = 0, EMPTY = kStages, FULL_C = 2 * kStages, TFULL = 3 * kStages, TEMPTY = 3 * kStages + 1;
 
     // both CTAs of the pair are resident before either touches the other's shared or tensor memory
     cluster_sync_all();
@@ -369,10 +378,8 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
             mbar_init(bar(EMPTY + s), 1);
             mbar_init(bar(FULL_C + s), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar(TFULL + b), 1);
-            mbar_init(bar(TEMPTY + b), 2 * kNumEpilogueWarps * 32);
-        }
+        mbar_init(bar(TFULL), 1);
+        mbar_init(bar(TEMPTY), 2 * kNumEpilogueWarps * 32);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -398,7 +405,7 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
                 const int td = tile % p.tiles_d, tq = tile / p.tiles_d;
-                const int q_row = tq * kPairRows + int(rank) * kTileRows, d_row = td * kPairRows + int(rank) * kTileRows;
+                const int q_row = tq * kPairRows + int(rank) * kTileRows, d_row = td * kPairDense + int(rank) * kDenseRows;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, abort_peer, (1 << 8) | (EMPTY + s));
                     if (!ok) break;
@@ -420,32 +427,36 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
             int s = 0;
             uint32_t ph = 0, local_tile = 0;
             bool ok = true;
-            const uint8_t* smem_a = p.quant_is_a ? smem_q : smem_d;
-            const uint8_t* smem_b = p.quant_is_a ? smem_d : smem_q;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++local_tile) {
-                const int buf = local_tile & 1;
-                const uint32_t tph = (local_tile >> 1) & 1;
-                ok = mbar_wait(bar(TEMPTY + buf), tph ^ 1, abort_flag, abort_peer, (2 << 8) | (TEMPTY + buf));
+                // both accumulators (TMEM columns [0,256) and [256,512)) belong to this tile: wait until the epilogue has
+                // moved the previous tile out
+                ok = mbar_wait(bar(TEMPTY), (local_tile & 1) ^ 1, abort_flag, abort_peer, (2 << 8) | TEMPTY);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + uint32_t(buf * kPairRows);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar(FULL + s), ph, abort_flag, abort_peer, (2 << 8) | (FULL + s));
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesQ);
-                    const uint32_t b_addr = smem_u32(smem_b + s * kStageBytesQ);
+                    const uint32_t q_addr = smem_u32(smem_q + s * kStageBytesQ);
+                    const uint32_t d_addr = smem_u32(smem_d + s * kStageBytesD);
+                    const uint32_t acc = (kb > 0) ? 1u : 0u;
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 16; ++k)
-                        umma_bf16_pair(d_tmem, make_smem_desc(a_addr + k * 32), make_smem_desc(b_addr + k * 32), kInstrDesc,
-                                       (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int h = 0; h < 2; ++h) {   // dense rows [128 h, 128 h + 128) of each CTA -> accumulator h
+                        const uint32_t dh = d_addr + uint32_t(h) * (128u * kBlockK * 2u);
+#pragma unroll
+                        for (int k = 0; k < kBlockK / 16; ++k) {
+                            const uint64_t qd = make_smem_desc(q_addr + k * 32), dd = make_smem_desc(dh + k * 32);
+                            if (p.quant_is_a)
+                                umma_bf16_pair(tmem_base + uint32_t(h * kPairRows), qd, dd, kInstrDesc, (k > 0) ? 1u : acc);
+                            else
+                                umma_bf16_pair(tmem_base + uint32_t(h * kPairRows), dd, qd, kInstrDesc, (k > 0) ? 1u : acc);
+                        }
+                    }
                     // the stage may be refilled, in both CTAs, once these MMAs have read it
                     umma_commit_both(bar(EMPTY + s));
                     if (++s == kStages) { s = 0; ph ^= 1; }
                 }
-                if (ok) {  // accumulator complete: each CTA's epilogue reads its own 128 rows
-                    umma_commit_both(bar(TFULL + buf));
-                }
+                if (ok) umma_commit_both(bar(TFULL));  // accumulators complete: each CTA's epilogue reads its own 128 lanes
             }
         }
     } else if (warp < kFirstEpilogueWarp) {
@@ -516,8 +527,10 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         }
     } else {
         // ------------------------------------------------ epilogue
+        // Accumulator h (TMEM columns [256 h, 256 h + 256)) holds, per CTA, 128 rows of the A operand against 256 rows of the
+        // B operand.  Dense rows of a tile are split as CTA r: [256 r, 256 r + 256), of which MMA group h took [128 h, +128).
         const int ew = warp & 3;                 // TMEM lane quadrant this warp may read
-        const int r_in_tile = ew * 32 + lane;    // accumulator row of this CTA = row of the A operand
+        const int r_in_tile = ew * 32 + lane;
         const int64_t rows_a = p.quant_is_a ? p.R_q : p.R_d, rows_b = p.quant_is_a ? p.R_d : p.R_q;
         const bool out_vec = (rows_b % 16 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 31) == 0) &&
                              ((reinterpret_cast<uintptr_t>(p.bias) & 3) == 0);
@@ -525,53 +538,63 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++local_tile) {
             const int tq = tile / p.tiles_d, td = tile % p.tiles_d;
-            const int ta = p.quant_is_a ? tq : td, tb = p.quant_is_a ? td : tq;
-            const int buf = local_tile & 1;
-            const uint32_t tph = (local_tile >> 1) & 1;
             // warp-uniform verdict: tcgen05.ld is a warp-wide instruction
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(TFULL + buf), tph, abort_flag, abort_peer, (4 << 8) | (TFULL + buf)));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(TFULL), local_tile & 1, abort_flag, abort_peer, (4 << 8) | TFULL));
             if (!ok) break;
             tc_fence_after();
-            const int64_t row = int64_t(ta) * kPairRows + int64_t(rank) * kTileRows + r_in_tile;
-            const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(buf * kPairRows);
+            {
+                const int h = (warp - kFirstEpilogueWarp) >> 2;   // one warp per lane quadrant and accumulator
+                // output row of this lane and first output column of accumulator column 0 / 128
+                int64_t row, col_lo, col_hi;
+                if (p.quant_is_a) {
+                    row = int64_t(tq) * kPairRows + int64_t(rank) * kTileRows + r_in_tile;
+                    col_lo = int64_t(td) * kPairDense + 128 * h;           // B rows held by CTA 0
+                    col_hi = col_lo + kDenseRows;                           // B rows held by CTA 1
+                } else {
+                    row = int64_t(td) * kPairDense + int64_t(rank) * kDenseRows + 128 * h + r_in_tile;
+                    col_lo = int64_t(tq) * kPairRows;
+                    col_hi = col_lo + kTileRows;
+                }
+                const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(h * kPairRows);
 #pragma unroll 1
-            for (int c = 0; c < kPairRows / 32; ++c) {
-                const int64_t col0 = int64_t(tb) * kPairRows + c * 32;
-                if (col0 >= rows_b) break;   // warp-uniform: the rest of the tile is outside the output
-                uint32_t v[32];
-                tmem_ld32(taddr0 + uint32_t(c * 32), v);
-                tmem_ld_wait();
-                if (row < rows_a) {
-                    uint16_t* dst = p.out + row * rows_b + col0;
-                    if (out_vec && col0 + 32 <= rows_b) {
+                for (int c = 0; c < kPairRows / 32; ++c) {
+                    const int64_t col0 = (c < 4 ? col_lo : col_hi) + (c & 3) * 32;
+                    if (col0 >= rows_b) continue;   // warp-uniform: this block of columns is outside the output
+                    uint32_t v[32];
+                    tmem_ld32(taddr0 + uint32_t(c * 32), v);
+                    tmem_ld_wait();
+                    if (row < rows_a) {
+                        uint16_t* dst = p.out + row * rows_b + col0;
+                        if (out_vec && col0 + 32 <= rows_b) {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            uint32_t w[8];
+                            for (int hh = 0; hh < 2; ++hh) {
+                                uint32_t w[8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                float a = __uint_as_float(v[16 * h + 2 * i]), b = __uint_as_float(v[16 * h + 2 * i + 1]);
-                                if (p.bias) {
-                                    const uint32_t bb = __ldg(reinterpret_cast<const uint32_t*>(p.bias + col0) + 8 * h + i);
-                                    a += __uint_as_float(bb << 16);
-                                    b += __uint_as_float(bb & 0xFFFF0000u);
+                                for (int i = 0; i < 8; ++i) {
+                                    float a = __uint_as_float(v[16 * hh + 2 * i]), b = __uint_as_float(v[16 * hh + 2 * i + 1]);
+                                    if (p.bias) {
+                                        const uint32_t bb = __ldg(reinterpret_cast<const uint32_t*>(p.bias + col0) + 8 * hh + i);
+                                        a += __uint_as_float(bb << 16);
+                                        b += __uint_as_float(bb & 0xFFFF0000u);
+                                    }
+                                    w[i] = pack_bf16(a, b);
                                 }
-                                w[i] = pack_bf16(a, b);
+                                st_global_v8(dst + 16 * hh, w);
                             }
-                            st_global_v8(dst + 16 * h, w);
-                        }
-                    } else {
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (col0 + i < rows_b) {
-                                float a = __uint_as_float(v[i]);
-                                if (p.bias) a += __uint_as_float(uint32_t(p.bias[col0 + i]) << 16);
-                                dst[i] = f32_to_bf16_bits(a);
-                            }
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < rows_b) {
+                                    float a = __uint_as_float(v[i]);
+                                    if (p.bias) a += __uint_as_float(uint32_t(p.bias[col0 + i]) << 16);
+                                    dst[i] = f32_to_bf16_bits(a);
+                                }
+                        }
                     }
                 }
             }
             tc_fence_before();
-            mbar_arrive_cluster(leader_bar(TEMPTY + buf));  // this accumulator may be overwritten
+            mbar_arrive_cluster(leader_bar(TEMPTY));  // the accumulators may be overwritten
         }
     }
 
@@ -648,7 +671,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
         return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales, bias and out must be 2-byte aligned", who);
     if (R_d > (int64_t(1) << 31) - 1 || R_q > (int64_t(1) << 31) - 1 || K > (int64_t(1) << 31) - 1)
         return tcb::fail(TCB_ERR_TOO_LARGE, "%s: dimension beyond 2^31 - 1", who);
-    const int64_t tiles_q = (R_q + kPairRows - 1) / kPairRows, tiles_d = (R_d + kPairRows - 1) / kPairRows;
+    const int64_t tiles_q = (R_q + kPairRows - 1) / kPairRows, tiles_d = (R_d + kPairDense - 1) / kPairDense;
     if (tiles_q * tiles_d > (int64_t(1) << 30)) return tcb::fail(TCB_ERR_TOO_LARGE, "%s: too many output tiles", who);
 
     EncodeTiledFn encode = encode_tiled_fn();
@@ -657,7 +680,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     CUtensorMap map;
     const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(R_d)};
     const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
-    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileRows)};
+    const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kDenseRows)};
     const cuuint32_t estr[2] = {1, 1};
     CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(dense), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
