@@ -25,7 +25,9 @@
 // tile, the expensive one to make, is used against twice as many dense rows.  The price
 // is that both accumulators belong to one tile, so the epilogue no longer overlaps the
 // next tile's MMAs; the eight epilogue warps hand the accumulators back as soon as they
-// have read them.
+// have read them.  Tiles that would make up a last, less than half full round of the CTA
+// pairs (and an odd last 256-row unit of the dense operand) run as 256 x 256 tiles on one
+// accumulator instead, side by side on twice as many pairs.
 //
 // Which operand is the M side depends on the wanted output layout, so that every
 // epilogue store is a row-contiguous vector store:
@@ -64,6 +66,7 @@
 // in the kernel blocks without such a bound (in particular no setmaxnreg, whose .inc
 // form waits for registers another warp group has to give up).
 #include <atomic>
+#include <type_traits>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -77,7 +80,6 @@ constexpr int kPairRows = 256;   // rows of each operand per CTA pair and tile (
 constexpr int kBlockK = 64;      // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kStages = 3;
 constexpr int kDenseRows = 256;  // dense rows per CTA and tile: two MMA groups of 128
-constexpr int kPairDense = 512;  // dense rows per CTA pair and tile
 constexpr int kNumProducerWarps = 8;
 constexpr int kNumEpilogueWarps = 8;
 constexpr int kThreads = 32 * (2 + kNumProducerWarps + kNumEpilogueWarps);  // 576
@@ -191,12 +193,24 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// The four MMAs (K = 16 each) of one 64-wide K step on one accumulator, issued back to back from one asm block: the
+// descriptors advance by 32 bytes (2 in their 16-byte address field) per MMA, only the first one may overwrite the
+// accumulator.  hi words of the descriptors are the same for every operand tile of this kernel.
+__device__ __forceinline__ void umma_bf16_pair_x4(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                                  uint32_t accumulate_first) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p, t;\n\t.reg .b64 a, b;\n\t.reg .b32 al, bl;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.eq.b32 t, %5, %5;\n\t"
+        "mov.b64 a, {%1, %3};\n\tmov.b64 b, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %4, p;\n\t"
+        "add.u32 al, %1, 2;\n\tadd.u32 bl, %2, 2;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %4, t;\n\t"
+        "add.u32 al, %1, 4;\n\tadd.u32 bl, %2, 4;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %4, t;\n\t"
+        "add.u32 al, %1, 6;\n\tadd.u32 bl, %2, 6;\n\tmov.b64 a, {al, %3};\n\tmov.b64 b, {bl, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], a, b, %4, t;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
 // Arrival on the barrier at offset `bar` of BOTH CTAs of the pair once every MMA this thread has issued so far has completed.
@@ -225,16 +239,11 @@ __device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
                  : "memory");
 }
 
-// K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
-    d |= uint64_t(1) << 16;                     // leading byte offset (unused with swizzle), 16-byte units
-    d |= uint64_t(1024 >> 4) << 32;             // stride byte offset between 8-row groups
-    d |= uint64_t(1) << 46;                     // descriptor version for sm_100
-    d |= uint64_t(2) << 61;                     // layout: 128-byte swizzle
-    return d;
-}
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Low word: start address in 16-byte units (14 bits) and the (unused) leading byte offset 1 at bit 16; high word: stride
+// byte offset 1024 >> 4, descriptor version 1 (bit 46 of the 64), layout type 2 = 128-byte swizzle (bits 61..63).
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
 
 // bf16 x bf16 -> fp32, A and B K-major, M = 256 (128 rows per CTA of the pair), N = 256
 constexpr uint32_t kInstrDesc =
@@ -252,7 +261,15 @@ struct Params {
     int64_t gpr;              // groups per row = K / G
     int table_vec_ok;         // scales / zero points of a table can be fetched with 16-byte loads
     int quant_is_a;           // the dequantised operand is the M side (output rows); otherwise the dense one is
-    int tiles_q, tiles_d;     // pair tiles (256 rows) along each operand
+    // Tile list of a launch.  Dense rows are counted in units of 256.  Tiles [0, n_wide) are wide (256 x 512: dense units
+    // 2j, 2j + 1); the next 2 n_conv tiles are the halves (256 x 256) of the wide tiles that would have made up a last,
+    // less than half full round of the CTA pairs; if the number of dense units is odd, one half tile per row of tiles
+    // covers the last unit.
+    int tiles_q;              // 256-row tiles along the quantised operand
+    int units_d;              // 256-row units along the dense operand
+    int wide_cols;            // units_d / 2
+    int n_wide, n_conv, n_odd;
+    int num_tiles;            // n_wide + 2 n_conv + n_odd
 };
 
 // Scales and zero points reach the producers through a shared-memory table that covers
@@ -343,11 +360,37 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v) {
     return *reinterpret_cast<uint16_t*>(&b);
 }
 
+struct Tile {
+    int tq;       // tile row along the quantised operand
+    int d_unit;   // first 256-row unit of the dense operand
+    int half;     // 1: a 256 x 256 tile (one accumulator, 128 dense rows per CTA)
+};
+
+__device__ __forceinline__ Tile decode_tile(const Params& p, int t) {
+    Tile r;
+    if (t < p.n_wide) {
+        r.half = 0;
+        r.tq = t / p.wide_cols;
+        r.d_unit = 2 * (t % p.wide_cols);
+    } else if (t < p.n_wide + 2 * p.n_conv) {
+        const int u = t - p.n_wide, w = p.n_wide + (u >> 1);
+        r.half = 1;
+        r.tq = w / p.wide_cols;
+        r.d_unit = 2 * (w % p.wide_cols) + (u & 1);
+    } else {
+        r.half = 1;
+        r.tq = t - p.n_wide - 2 * p.n_conv;
+        r.d_unit = p.units_d - 1;
+    }
+    return r;
+}
+
 // -------------------------------------------------------------------- kernel
 
 template <int LOG2_G, bool HAS_ZP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const __grid_constant__ CUtensorMap code_map, const Params p) {
+fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const __grid_constant__ CUtensorMap dense_map_half,
+                          const __grid_constant__ CUtensorMap code_map, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_q = smem;                                   // kStages x 16 KB, dequantised operand
@@ -394,7 +437,7 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
 
     const int num_kb = int((p.K + kBlockK - 1) / kBlockK);  // a ragged last K block is zero-filled by the TMA (dense tile and
                                                             // codes) and gets zero scales from the table fetch
-    const int num_tiles = p.tiles_q * p.tiles_d;
+    const int num_tiles = p.num_tiles;
     const int first_tile = int(blockIdx.x >> 1), tile_step = int(gridDim.x >> 1);
 
     if (warp == 0) {
@@ -404,17 +447,20 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-                const int td = tile % p.tiles_d, tq = tile / p.tiles_d;
-                const int q_row = tq * kPairRows + int(rank) * kTileRows, d_row = td * kPairDense + int(rank) * kDenseRows;
+                const Tile t = decode_tile(p, tile);
+                const int q_row = t.tq * kPairRows + int(rank) * kTileRows;
+                const int d_row = t.d_unit * kPairRows + int(rank) * (t.half ? kTileRows : kDenseRows);
+                const CUtensorMap* dmap = t.half ? &dense_map_half : &dense_map;
+                const uint32_t d_bytes = t.half ? kStageBytesD / 2 : kStageBytesD;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(bar(EMPTY + s), ph ^ 1, abort_flag, abort_peer, (1 << 8) | (EMPTY + s));
                     if (!ok) break;
                     mbar_arrive_expect_tx(bar(FULL_C + s), kStageBytesC);
                     tma_load_2d(smem_u32(smem_c + s * kStageBytesC), &code_map, kb * kBlockK, q_row, bar(FULL_C + s));
                     const uint32_t fd = leader_bar(FULL + s);
-                    tma_load_2d_pair(smem_u32(smem_d + s * kStageBytesD), &dense_map, kb * kBlockK, d_row, fd);
+                    tma_load_2d_pair(smem_u32(smem_d + s * kStageBytesD), dmap, kb * kBlockK, d_row, fd);
                     if (leader)
-                        mbar_arrive_expect_tx(bar(FULL + s), 2 * kStageBytesD);
+                        mbar_arrive_expect_tx(bar(FULL + s), 2 * d_bytes);
                     else
                         mbar_arrive_cluster(fd);
                     if (++s == kStages) { s = 0; ph ^= 1; }
@@ -433,28 +479,35 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
                 ok = mbar_wait(bar(TEMPTY), (local_tile & 1) ^ 1, abort_flag, abort_peer, (2 << 8) | TEMPTY);
                 if (!ok) break;
                 tc_fence_after();
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(bar(FULL + s), ph, abort_flag, abort_peer, (2 << 8) | (FULL + s));
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t q_addr = smem_u32(smem_q + s * kStageBytesQ);
-                    const uint32_t d_addr = smem_u32(smem_d + s * kStageBytesD);
-                    const uint32_t acc = (kb > 0) ? 1u : 0u;
+                // the K loop, once per tile kind, so that the issue sequence of a stage has no branch in it
+                const uint32_t q_lo0 = smem_desc_lo(smem_u32(smem_q)), d_lo0 = smem_desc_lo(smem_u32(smem_d));
+                auto k_loop = [&](auto groups_tag, auto quant_is_a_tag) {
+                    constexpr int kGroups = decltype(groups_tag)::value;   // MMA groups per stage: 2 (wide tile) or 1
+                    constexpr bool kQuantIsA = decltype(quant_is_a_tag)::value;
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        ok = mbar_wait(bar(FULL + s), ph, abort_flag, abort_peer, (2 << 8) | (FULL + s));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t q_lo = q_lo0 + uint32_t(s) * (kStageBytesQ >> 4);
+                        const uint32_t d_lo = d_lo0 + uint32_t(s) * (kStageBytesD >> 4);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {   // dense rows [128 h, 128 h + 128) of each CTA -> accumulator h
-                        const uint32_t dh = d_addr + uint32_t(h) * (128u * kBlockK * 2u);
-#pragma unroll
-                        for (int k = 0; k < kBlockK / 16; ++k) {
-                            const uint64_t qd = make_smem_desc(q_addr + k * 32), dd = make_smem_desc(dh + k * 32);
-                            if (p.quant_is_a)
-                                umma_bf16_pair(tmem_base + uint32_t(h * kPairRows), qd, dd, kInstrDesc, (k > 0) ? 1u : acc);
-                            else
-                                umma_bf16_pair(tmem_base + uint32_t(h * kPairRows), dd, qd, kInstrDesc, (k > 0) ? 1u : acc);
+                        for (int h = 0; h < kGroups; ++h) {   // dense rows [128 h, 128 h + 128) of each CTA -> accumulator h
+                            const uint32_t dh = d_lo + uint32_t(h) * ((128u * kBlockK * 2u) >> 4);
+                            umma_bf16_pair_x4(tmem_base + uint32_t(h * kPairRows), kQuantIsA ? q_lo : dh, kQuantIsA ? dh : q_lo, kDescHi,
+                                              kInstrDesc, kb > 0 ? 1u : 0u);
                         }
+                        // the stage may be refilled, in both CTAs, once these MMAs have read it
+                        umma_commit_both(bar(EMPTY + s));
+                        if (++s == kStages) { s = 0; ph ^= 1; }
                     }
-                    // the stage may be refilled, in both CTAs, once these MMAs have read it
-                    umma_commit_both(bar(EMPTY + s));
-                    if (++s == kStages) { s = 0; ph ^= 1; }
+                };
+                const bool half = decode_tile(p, tile).half != 0;
+                if (p.quant_is_a) {
+                    if (half) k_loop(std::integral_constant<int, 1>(), std::true_type());
+                    else k_loop(std::integral_constant<int, 2>(), std::true_type());
+                } else {
+                    if (half) k_loop(std::integral_constant<int, 1>(), std::false_type());
+                    else k_loop(std::integral_constant<int, 2>(), std::false_type());
                 }
                 if (ok) umma_commit_both(bar(TFULL));  // accumulators complete: each CTA's epilogue reads its own 128 lanes
             }
@@ -482,7 +535,7 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         TableRegs regs;
         auto fetch_next_table = [&]() {
             if (pf_tile < num_tiles) {
-                const int64_t grow = int64_t(pf_tile / p.tiles_d) * kPairRows + int64_t(rank) * kTileRows + fr;
+                const int64_t grow = int64_t(decode_tile(p, pf_tile).tq) * kPairRows + int64_t(rank) * kTileRows + fr;
                 table_fetch(p, grow, int64_t(pf_table) * kTableGroups + fh * 16, grow < p.R_q, regs);
             }
             if (++pf_table == tables_per_tile) {
@@ -537,7 +590,7 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         uint32_t local_tile = 0;
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++local_tile) {
-            const int tq = tile / p.tiles_d, td = tile % p.tiles_d;
+            const Tile t = decode_tile(p, tile);
             // warp-uniform verdict: tcgen05.ld is a warp-wide instruction
             ok = __all_sync(0xffffffffu, mbar_wait(bar(TFULL), local_tile & 1, abort_flag, abort_peer, (4 << 8) | TFULL));
             if (!ok) break;
@@ -546,20 +599,21 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
                 const int h = (warp - kFirstEpilogueWarp) >> 2;   // one warp per lane quadrant and accumulator
                 // output row of this lane and first output column of accumulator column 0 / 128
                 int64_t row, col_lo, col_hi;
+                const int dense_per_cta = t.half ? kTileRows : kDenseRows;
                 if (p.quant_is_a) {
-                    row = int64_t(tq) * kPairRows + int64_t(rank) * kTileRows + r_in_tile;
-                    col_lo = int64_t(td) * kPairDense + 128 * h;           // B rows held by CTA 0
-                    col_hi = col_lo + kDenseRows;                           // B rows held by CTA 1
+                    row = int64_t(t.tq) * kPairRows + int64_t(rank) * kTileRows + r_in_tile;
+                    col_lo = int64_t(t.d_unit) * kPairRows + 128 * h;      // B rows held by CTA 0
+                    col_hi = col_lo + dense_per_cta;                        // B rows held by CTA 1
                 } else {
-                    row = int64_t(td) * kPairDense + int64_t(rank) * kDenseRows + 128 * h + r_in_tile;
-                    col_lo = int64_t(tq) * kPairRows;
+                    row = int64_t(t.d_unit) * kPairRows + int64_t(rank) * dense_per_cta + 128 * h + r_in_tile;
+                    col_lo = int64_t(t.tq) * kPairRows;
                     col_hi = col_lo + kTileRows;
                 }
                 const uint32_t taddr0 = tmem_base + (uint32_t(ew * 32) << 16) + uint32_t(h * kPairRows);
 #pragma unroll 1
                 for (int c = 0; c < kPairRows / 32; ++c) {
                     const int64_t col0 = (c < 4 ? col_lo : col_hi) + (c & 3) * 32;
-                    if (col0 >= rows_b) continue;   // warp-uniform: this block of columns is outside the output
+                    if (col0 >= rows_b || h >= (t.half ? 1 : 2)) continue;   // warp-uniform: outside the output, or an unused accumulator
                     uint32_t v[32];
                     tmem_ld32(taddr0 + uint32_t(c * 32), v);
                     tmem_ld_wait();
@@ -671,13 +725,14 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
         return tcb::fail(TCB_ERR_ALIGNMENT, "%s: scales, bias and out must be 2-byte aligned", who);
     if (R_d > (int64_t(1) << 31) - 1 || R_q > (int64_t(1) << 31) - 1 || K > (int64_t(1) << 31) - 1)
         return tcb::fail(TCB_ERR_TOO_LARGE, "%s: dimension beyond 2^31 - 1", who);
-    const int64_t tiles_q = (R_q + kPairRows - 1) / kPairRows, tiles_d = (R_d + kPairDense - 1) / kPairDense;
-    if (tiles_q * tiles_d > (int64_t(1) << 30)) return tcb::fail(TCB_ERR_TOO_LARGE, "%s: too many output tiles", who);
+    const int64_t tiles_q = (R_q + kPairRows - 1) / kPairRows, units_d = (R_d + kPairRows - 1) / kPairRows;
+    if (tiles_q * units_d > (int64_t(1) << 30)) return tcb::fail(TCB_ERR_TOO_LARGE, "%s: too many output tiles", who);
 
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
-    // dense operand: [R_d, K] bf16, one box = the 128 rows x 64 columns a CTA stages per K step
-    CUtensorMap map;
+    // dense operand: [R_d, K] bf16, one box = the 256 rows x 64 columns a CTA stages per K step of a wide tile
+    // (a second map with 128-row boxes serves the 256 x 256 tiles)
+    CUtensorMap map, map_half;
     const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(R_d)};
     const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
     const cuuint32_t box[2] = {cuuint32_t(kBlockK), cuuint32_t(kDenseRows)};
@@ -686,6 +741,11 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", who, int(cr));
+    const cuuint32_t box_half[2] = {cuuint32_t(kBlockK), cuuint32_t(kTileRows)};
+    cr = encode(&map_half, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(dense), dims, strides, box_half, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled (half tiles) failed with %d", who, int(cr));
     // raw codes: [R_q, K] bytes, 64-byte rows in shared memory, no swizzle (read by the producer warps)
     CUtensorMap cmap;
     const cuuint64_t cdims[2] = {cuuint64_t(K), cuuint64_t(R_q)};
@@ -697,7 +757,7 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     if (cr != CUDA_SUCCESS) return tcb::fail(TCB_ERR_CUDA, "%s: cuTensorMapEncodeTiled (codes) failed with %d", who, int(cr));
 
     // one instantiation per (group size, zero points or not): those are compile-time in the producer warps
-    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const Params);
+    typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
     static const KernelFn kernels[3][2] = {
         {fused_dequant_gemm_kernel<4, false>, fused_dequant_gemm_kernel<4, true>},
         {fused_dequant_gemm_kernel<5, false>, fused_dequant_gemm_kernel<5, true>},
@@ -725,12 +785,22 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
     p.table_vec_ok = p.gpr % 16 == 0 && (reinterpret_cast<uintptr_t>(scales) & 15) == 0 &&
                      (zp_or_null == nullptr || (reinterpret_cast<uintptr_t>(zp_or_null) & 15) == 0);
     p.quant_is_a = quant_is_rhs ? 0 : 1;
-    p.tiles_q = int(tiles_q);
-    p.tiles_d = int(tiles_d);
-    const int64_t num_tiles = tiles_q * tiles_d;
+    // The tile list: wide (256 x 512) tiles as far as they fill whole rounds of the CTA pairs; if what is left of them
+    // would occupy at most half of the pairs for a last round, those become twice as many 256 x 256 tiles, which run
+    // side by side in half the time; an odd last dense unit is covered by 256 x 256 tiles as well.
     const int pairs = tcb::sm_count() / 2 > 0 ? tcb::sm_count() / 2 : 1;
-    const int grid = 2 * int(num_tiles < pairs ? num_tiles : pairs);   // a cluster of two CTAs per tile in flight
-    kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, cmap, p);
+    const int64_t wide_cols = units_d / 2, wide_total = tiles_q * wide_cols;
+    const int64_t last_round = wide_total % pairs;
+    const int64_t n_conv = (last_round > 0 && 2 * last_round <= pairs) ? last_round : 0;
+    p.tiles_q = int(tiles_q);
+    p.units_d = int(units_d);
+    p.wide_cols = int(wide_cols);
+    p.n_wide = int(wide_total - n_conv);
+    p.n_conv = int(n_conv);
+    p.n_odd = (units_d & 1) ? int(tiles_q) : 0;
+    p.num_tiles = p.n_wide + 2 * p.n_conv + p.n_odd;
+    const int grid = 2 * (p.num_tiles < pairs ? p.num_tiles : pairs);   // a cluster of two CTAs per tile in flight
+    kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map, map_half, cmap, p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TCB_OK : tcb::cuda_fail(e, who);
 }
