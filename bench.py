@@ -316,32 +316,45 @@ def shared_scratch(rank: int, barrier, need_bytes: int):
 
 
 def write_sharded_cache(tc, prefix: str, total: int, n_shards: int, rank: int, world: int, device, barrier):
-    """All ranks fill ONE `n_shards`-way cache of `total` samples: rank r writes the shards i with i % world == r through
-    FeatureCacheWriter.for_shard, rank 0 adds the manifest.  Returns (samples/s of this rank's append calls, spot-check)."""
+    """All ranks fill ONE `n_shards`-way cache of `total` samples.  One rank: the reference's own call,
+    FeatureCacheWriter(prefix, total, ..., num_shards=n_shards).  Several ranks: rank r writes the shards i with
+    i % world == r through FeatureCacheWriter.for_shard (all of them opened before the first append), rank 0 adds the
+    manifest.  The rank's samples are generated on the device BEFORE the clock starts; the clock runs from before the
+    writer(s) are opened until the last one is closed.  Returns (samples/s of this rank, spot-check)."""
     kw = dict(group_size=G, amo_bq=True, amo_mode="balanced")
     base, rem = divmod(total, n_shards)
     sizes = [base + (1 if i < rem else 0) for i in range(n_shards)]
     offsets = np.cumsum([0] + sizes[:-1])
-    spent, written = 0.0, 0
+    mine = list(range(rank, n_shards, world))
     BLOCK = 2048   # samples per append call (1.4 GB of bf16): eight 256-sample encode chunks in flight behind one another
-    for i in range(rank, n_shards, world):
-        w = tc.FeatureCacheWriter.for_shard(prefix, i, total, SHAPE[1], SHAPE[2], n_shards, **kw)
-        pos = 0
-        while pos < sizes[i]:
+    data = {}
+    for i in mine:
+        buf = torch.empty((sizes[i], SHAPE[1], SHAPE[2]), dtype=torch.bfloat16, device=device)
+        for pos in range(0, sizes[i], BLOCK):
             n = min(BLOCK, sizes[i] - pos)
-            x = feature_slice(device, 4, int(offsets[i]) + pos, n)
-            torch.cuda.synchronize(device)
-            t0 = time.perf_counter()
-            w.append(x)
-            spent += time.perf_counter() - t0
-            written += n
-            pos += n
-            del x
-        t0 = time.perf_counter()
-        w.close()
-        spent += time.perf_counter() - t0
+            buf[pos:pos + n] = feature_slice(device, 4, int(offsets[i]) + pos, n)
+        data[i] = buf
+    torch.cuda.synchronize(device)
     barrier()
-    if rank == 0:
+    written = sum(sizes[i] for i in mine)
+    t0 = time.perf_counter()
+    if world == 1:
+        w = tc.FeatureCacheWriter(prefix, total, SHAPE[1], SHAPE[2], num_shards=n_shards, **kw)
+        for i in mine:
+            for pos in range(0, sizes[i], BLOCK):
+                w.append(data[i][pos:pos + BLOCK])
+        w.close()
+    else:
+        writers = {i: tc.FeatureCacheWriter.for_shard(prefix, i, total, SHAPE[1], SHAPE[2], n_shards, **kw) for i in mine}
+        for i in mine:
+            for pos in range(0, sizes[i], BLOCK):
+                writers[i].append(data[i][pos:pos + BLOCK])
+            writers[i].close()
+    spent = time.perf_counter() - t0
+    data.clear()
+    torch.cuda.empty_cache()
+    barrier()
+    if rank == 0 and world > 1:
         tc.FeatureCacheWriter.write_manifest(prefix, total, SHAPE[1], SHAPE[2], n_shards, **kw)
     barrier()
     # spot check: the first 256 rows of every shard this rank wrote against compress() of the regenerated samples
@@ -865,7 +878,9 @@ def main():
                     "note": "default_* = pin_shard=None (what a drop-in user gets); staging_* = pin_shard=False (rows copied into "
                             "page-locked staging by worker threads, the reference's scheme); iter_batches = FeatureCacheDataset.iter_batches"}
         c4 = {"samples": total, "shards": C4_SHARDS, "bytes": total * BYTES_PER_SAMPLE,
-              "written_by": f"{world} rank(s), FeatureCacheWriter.for_shard for shard i on rank i % {world}, manifest by rank 0",
+              "written_by": ("1 rank, FeatureCacheWriter(prefix, total, 446, 768, amo_bq=True, amo_mode='balanced', num_shards=8)" if world == 1
+                             else f"{world} ranks, FeatureCacheWriter.for_shard for shard i on rank i % {world}, manifest by rank 0")
+                            + "; samples on the device beforehand, clock from opening the writer to its close",
               "full_size": total == C4_SAMPLES, "spot_check": {"rows_per_shard": 256, "bit_equal_with_compress": spot_ok},
               "rank_to_shards": f"rank r reads the shards i with i % {world} == r (identical to shard r % 8 of the reference at 8 ranks)"}
 

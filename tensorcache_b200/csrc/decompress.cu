@@ -231,9 +231,11 @@ decompress_vec_kernel(const uint4* __restrict__ q, const uint16_t* __restrict__ 
 
 // Group sizes that are a multiple of 8 but not a power of two >= 16 (8, 24, 48), 32-byte aligned
 // pointers: the main kernel's data movement (32 codes per thread, one 256-bit load, two 256-bit
-// stores) with one scale / zero point per octet of codes, since a thread's four octets can belong to
-// up to four groups.  OPG = octets per group.
-template <int OPG, bool SYM>
+// stores) with one scale / zero point per octet of codes.  OPG = octets per group.  A thread's four
+// octets belong to four groups at G = 8 and to at most two neighbouring groups at G = 24 / 48, so the
+// scales and zero points come in one 64-bit + one 32-bit load (G = 8, VEC_META: scales 8-byte and zero
+// points 4-byte aligned) or in two loads of each (G = 24 / 48) instead of four scalar loads of each.
+template <int OPG, bool SYM, bool VEC_META>
 __global__ void __launch_bounds__(kThreads)
 decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zp,
                          uint16_t* __restrict__ out, int64_t numel) {
@@ -253,11 +255,29 @@ decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
             const int64_t t = t0 + int64_t(u) * kThreads;
             if (t < end) {
                 ldg_stream_v8(q + (t << 5), w[u]);
+                if (OPG == 1 && VEC_META) {
+                    const uint2 s4 = __ldg(reinterpret_cast<const uint2*>(scales + 4 * t));
+                    const uint32_t z4 = SYM ? kSignFlip : __ldg(reinterpret_cast<const uint32_t*>(zp + 4 * t));
+                    sb[u][0] = uint16_t(s4.x), sb[u][1] = uint16_t(s4.x >> 16), sb[u][2] = uint16_t(s4.y), sb[u][3] = uint16_t(s4.y >> 16);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int64_t g = (4 * t + j) / OPG;
-                    sb[u][j] = __ldg(scales + g);
-                    zb[u][j] = SYM ? uint8_t(128) : __ldg(zp + g);
+                    for (int j = 0; j < 4; ++j) zb[u][j] = uint8_t(z4 >> (8 * j));
+                } else if (OPG == 1) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        sb[u][j] = __ldg(scales + 4 * t + j);
+                        zb[u][j] = SYM ? uint8_t(128) : __ldg(zp + 4 * t + j);
+                    }
+                } else {
+                    const int64_t g0 = (4 * t) / OPG;
+                    const int first = int((g0 + 1) * OPG - 4 * t);  // this thread's octets [0, first) are of group g0, the rest of g0 + 1
+                    const bool two = first < 4;
+                    const uint16_t s0 = __ldg(scales + g0), s1 = two ? __ldg(scales + g0 + 1) : s0;
+                    const uint8_t z0 = SYM ? uint8_t(128) : __ldg(zp + g0), z1 = (SYM || !two) ? z0 : __ldg(zp + g0 + 1);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        sb[u][j] = j < first ? s0 : s1;
+                        zb[u][j] = j < first ? z0 : z1;
+                    }
                 }
                 if (SYM) {
 #pragma unroll
@@ -432,8 +452,15 @@ cudaError_t prime_amo_variants() {
 template <int OPG, bool SYM>
 cudaError_t launch_oct(const uint8_t* q, const uint16_t* s, const uint8_t* zp, uint16_t* out, int64_t numel, bool aligned32,
                        cudaStream_t st) {
-    static WaveCache cache, cache32;
-    if (aligned32) return launch_one_wave(decompress_v8_oct_kernel<OPG, SYM>, cache32, numel >> 5, q, s, zp, out, numel, st);
+    static WaveCache cache, cache32, cache32v;
+    if (aligned32) {
+        if constexpr (OPG == 1) {
+            const bool vec_meta = (reinterpret_cast<uintptr_t>(s) & 7) == 0 && (SYM || (reinterpret_cast<uintptr_t>(zp) & 3) == 0);
+            if (vec_meta)
+                return launch_one_wave(decompress_v8_oct_kernel<OPG, SYM, true>, cache32v, numel >> 5, q, s, zp, out, numel, st);
+        }
+        return launch_one_wave(decompress_v8_oct_kernel<OPG, SYM, false>, cache32, numel >> 5, q, s, zp, out, numel, st);
+    }
     return launch_one_wave(decompress_oct_kernel<OPG, SYM>, cache, numel >> 3, reinterpret_cast<const uint2*>(q), s, zp, out,
                            numel, st);
 }

@@ -22,7 +22,8 @@ import torch
 import ctypes
 
 from . import _lib
-from ._pipeline import NativePipeline, open_cache, try_make_resident, writer_threads
+from ._pipeline import NativePipeline, _mem_available_bytes, open_cache, try_make_resident, writer_threads
+from ._prefault import MEM_FRACTION_FOR_PREFAULT, Prefaulter, in_memory_filesystem
 from .codec import AMO_BQ_PRESETS, BlockwiseInt8Codec, dequantize_int8_amo_bq, dequantize_int8_g32
 
 
@@ -34,6 +35,11 @@ class FeatureCacheWriter:
     through page-locked buffers, and rows are copied into the memory maps.  Each
     sample's codes equal ``compress(sample)`` because ``seq_len * dim`` must be a
     multiple of the group size (checked).
+
+    ``prefault`` (not in the reference): populate the pages of the new files in the background while the first
+    samples are still being encoded.  ``None`` = automatic: on when the files live in memory-backed storage and fit
+    half of the available memory, which is where first-touch page allocation bounds the writer; ``False`` leaves
+    the files sparse until rows land in them.
     """
 
     _CHUNK = 256  # samples per encode launch (the reference's CUDA path takes 64; every sample is encoded on
@@ -42,10 +48,25 @@ class FeatureCacheWriter:
     def __init__(self, output_prefix: Union[str, Path], num_samples: int, seq_len: int, dim: int,
                  group_size: int = 32, adaptive: bool = False, amo_bq: bool = False, amo_lo: float = 0.95,
                  amo_hi: float = 1.05, amo_candidates: int = 32, amo_mode: Optional[str] = None,
-                 num_shards: int = 1, quant_bits: int = 8, resume: bool = False):
+                 num_shards: int = 1, quant_bits: int = 8, resume: bool = False, prefault: Optional[bool] = None):
         self._resolve_settings(output_prefix, num_samples, seq_len, dim, group_size, adaptive, amo_bq, amo_lo, amo_hi,
                                amo_candidates, amo_mode, num_shards, quant_bits, resume)
         self._open_maps(resume)
+        self._start_prefault(prefault, resume)
+
+    def _start_prefault(self, wanted: Optional[bool], resume: bool) -> None:
+        self._prefaulter = None
+        if wanted is False or resume:      # an appended-to cache already has most of its pages
+            return
+        spans = [(int(mm.ctypes.data), int(mm.nbytes)) for maps in self._maps if maps is not None for mm in maps]
+        total = sum(n for _, n in spans)
+        if wanted is None:
+            avail = _mem_available_bytes()
+            if not in_memory_filesystem(self.shard_prefixes[0] + "_int8.bin") or avail is None or \
+                    total > MEM_FRACTION_FOR_PREFAULT * avail:
+                return
+        if total:
+            self._prefaulter = Prefaulter(spans)
 
     def _resolve_settings(self, output_prefix, num_samples, seq_len, dim, group_size, adaptive, amo_bq, amo_lo, amo_hi,
                           amo_candidates, amo_mode, num_shards, quant_bits, resume):
@@ -304,6 +325,9 @@ class FeatureCacheWriter:
         if getattr(self, "_closed", True):
             return
         self._closed = True
+        if getattr(self, "_prefaulter", None) is not None:
+            self._prefaulter.stop()     # no thread may touch a mapping that is about to go away
+            self._prefaulter = None
         for maps in self._maps:
             if maps is None:
                 continue

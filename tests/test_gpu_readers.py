@@ -322,3 +322,27 @@ def test_per_shard_writers_fill_the_same_cache_as_one_sharded_writer(tmp_path):
         assert np.array_equal(bits(torch.cat([b.clone() for b in st])).reshape(33, -1), want[34:67])
     with pytest.raises(ValueError):
         tc.FeatureCacheWriter.for_shard(tmp_path / "c" / "feat", 3, 100, 16, 128, 3, **kw)
+
+
+@pytest.mark.parametrize("prefault", [True, None])
+def test_background_page_population_changes_no_byte(tmp_path, prefault):
+    """A writer that populates its new files in the background (forced, and the automatic rule on memory-backed
+    storage) writes the same bytes as one that leaves the files sparse, also when it is closed before it is full."""
+    import os, shutil
+    x = synth.config0_style(45, (300, 16, 128))
+    kw = dict(group_size=32, amo_bq=True, amo_mode="balanced", num_shards=3)
+    shm = Path("/dev/shm") / f"tcb_prefault_cache_{os.getpid()}"
+    root = shm if (prefault is None and os.access("/dev/shm", os.W_OK)) else tmp_path / "p"
+    try:
+        plain = tc.FeatureCacheWriter(tmp_path / "a" / "feat", 400, 16, 128, prefault=False, **kw)
+        assert plain._prefaulter is None
+        plain.append(x.to(DEV)); plain.close()
+        w = tc.FeatureCacheWriter(root / "feat", 400, 16, 128, prefault=prefault, **kw)
+        assert (w._prefaulter is not None) == (prefault is True or root == shm)
+        w.append(x[:100].to(DEV)); w.append(x[100:]); w.close()      # 300 of 400 samples: the last shard stays partly empty
+        assert w._prefaulter is None
+        for f in sorted((tmp_path / "a").iterdir()):
+            if f.suffix == ".bin":
+                assert (root / f.name).read_bytes() == f.read_bytes(), f.name
+    finally:
+        shutil.rmtree(shm, ignore_errors=True)

@@ -208,3 +208,35 @@ def test_manifest_written_for_per_shard_writers_equals_the_reference_manifest(tm
         tc.FeatureCacheWriter.write_manifest(tmp_path / "single", 7, 6, 64, 1)
     with pytest.raises(TypeError):
         tc.FeatureCacheWriter.write_manifest(tmp_path / "bad", 7, 6, 64, 3, colour="red")
+
+
+def test_prefaulter_populates_new_files_in_the_background_without_changing_them(tmp_path):
+    """The writer's page population (madvise on the mappings of freshly created files): every page of every range ends
+    up allocated, existing bytes stay, a stopped populator leaves its threads joined."""
+    from tensorcache_b200._prefault import Prefaulter, filesystem_type, in_memory_filesystem
+    base = Path("/dev/shm") if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else tmp_path
+    folder = base / f"tcb_prefault_test_{os.getpid()}"
+    folder.mkdir()
+    try:
+        assert filesystem_type(str(folder)) is not None
+        if base != tmp_path:
+            assert in_memory_filesystem(str(folder / "a.bin"))
+        sizes = [5 << 20, (33 << 20) + 123, 4096]
+        maps = [np.memmap(folder / f"f{i}.bin", dtype=np.uint8, mode="w+", shape=(n,)) for i, n in enumerate(sizes)]
+        maps[0][:16] = np.arange(16, dtype=np.uint8)          # data that is already there survives
+        pf = Prefaulter([(int(m.ctypes.data), int(m.nbytes)) for m in maps], threads=3)
+        pf.stop()                                              # joins; whatever was not started stays unpopulated
+        assert pf.done()
+        pf = Prefaulter([(int(m.ctypes.data), int(m.nbytes)) for m in maps], threads=3)
+        for t in pf._threads:
+            t.join()
+        assert pf.done()
+        if not pf.failed:                                      # kernels before 5.14 refuse the advice; the writer then runs without
+            assert pf.populated == sum(sizes)
+            for i, n in enumerate(sizes):
+                assert os.stat(folder / f"f{i}.bin").st_blocks * 512 >= n
+        assert maps[0][:16].tolist() == list(range(16)) and int(maps[0][16:].max()) == 0 and int(maps[1].max()) == 0
+        pf.stop()
+        del maps
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
