@@ -248,8 +248,8 @@ decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
 
     for (int64_t t0 = begin + threadIdx.x; t0 < end; t0 += int64_t(kThreads) * kUnroll32) {
         uint32_t w[kUnroll32][8];
-        uint16_t sb[kUnroll32][4];
-        uint8_t zb[kUnroll32][4];
+        uint32_t ms[kUnroll32][2];   // the four octets' scales, two bf16 per word
+        uint32_t mz[kUnroll32];      // their zero points, one per byte
 #pragma unroll
         for (int u = 0; u < kUnroll32; ++u) {
             const int64_t t = t0 + int64_t(u) * kThreads;
@@ -257,27 +257,24 @@ decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
                 ldg_stream_v8(q + (t << 5), w[u]);
                 if (OPG == 1 && VEC_META) {
                     const uint2 s4 = __ldg(reinterpret_cast<const uint2*>(scales + 4 * t));
-                    const uint32_t z4 = SYM ? kSignFlip : __ldg(reinterpret_cast<const uint32_t*>(zp + 4 * t));
-                    sb[u][0] = uint16_t(s4.x), sb[u][1] = uint16_t(s4.x >> 16), sb[u][2] = uint16_t(s4.y), sb[u][3] = uint16_t(s4.y >> 16);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) zb[u][j] = uint8_t(z4 >> (8 * j));
+                    ms[u][0] = s4.x, ms[u][1] = s4.y;
+                    mz[u] = SYM ? kSignFlip : __ldg(reinterpret_cast<const uint32_t*>(zp + 4 * t));
                 } else if (OPG == 1) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        sb[u][j] = __ldg(scales + 4 * t + j);
-                        zb[u][j] = SYM ? uint8_t(128) : __ldg(zp + 4 * t + j);
-                    }
+                    ms[u][0] = uint32_t(__ldg(scales + 4 * t)) | uint32_t(__ldg(scales + 4 * t + 1)) << 16;
+                    ms[u][1] = uint32_t(__ldg(scales + 4 * t + 2)) | uint32_t(__ldg(scales + 4 * t + 3)) << 16;
+                    mz[u] = SYM ? kSignFlip
+                                : uint32_t(__ldg(zp + 4 * t)) | uint32_t(__ldg(zp + 4 * t + 1)) << 8 |
+                                      uint32_t(__ldg(zp + 4 * t + 2)) << 16 | uint32_t(__ldg(zp + 4 * t + 3)) << 24;
                 } else {
                     const int64_t g0 = (4 * t) / OPG;
                     const int first = int((g0 + 1) * OPG - 4 * t);  // this thread's octets [0, first) are of group g0, the rest of g0 + 1
                     const bool two = first < 4;
-                    const uint16_t s0 = __ldg(scales + g0), s1 = two ? __ldg(scales + g0 + 1) : s0;
-                    const uint8_t z0 = SYM ? uint8_t(128) : __ldg(zp + g0), z1 = (SYM || !two) ? z0 : __ldg(zp + g0 + 1);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        sb[u][j] = j < first ? s0 : s1;
-                        zb[u][j] = j < first ? z0 : z1;
-                    }
+                    const uint32_t s0 = __ldg(scales + g0), s1 = two ? uint32_t(__ldg(scales + g0 + 1)) : s0;
+                    const uint32_t z0 = SYM ? 128u : uint32_t(__ldg(zp + g0)), z1 = (SYM || !two) ? z0 : uint32_t(__ldg(zp + g0 + 1));
+                    // first is 1, 2, 3 or >= 4: octet j takes group g0 when j < first
+                    ms[u][0] = s0 | (first > 1 ? s0 : s1) << 16;
+                    ms[u][1] = (first > 2 ? s0 : s1) | (first > 3 ? s0 : s1) << 16;
+                    mz[u] = z0 | (first > 1 ? z0 : z1) << 8 | (first > 2 ? z0 : z1) << 16 | (first > 3 ? z0 : z1) << 24;
                 }
                 if (SYM) {
 #pragma unroll
@@ -294,8 +291,11 @@ decompress_v8_oct_kernel(const uint8_t* __restrict__ q, const uint16_t* __restri
                     uint32_t o[8];
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        const float scale = bf16_bits_to_float(sb[u][2 * h + j]);
-                        const float zmagic = 8388608.0f + float(zb[u][2 * h + j]);
+                        const int oct = 2 * h + j;
+                        // bf16 bits -> fp32 bits: the even octet's scale sits in the low half of its word
+                        const float scale = __uint_as_float((oct & 1) ? (ms[u][oct >> 1] & 0xFFFF0000u) : (ms[u][oct >> 1] << 16));
+                        // 2^23 + zp is exactly the fp32 whose low mantissa byte is zp
+                        const float zmagic = __uint_as_float(__byte_perm(mz[u], 0x4B000000u, 0x7650 + oct));
                         convert_word(w[u][4 * h + 2 * j], zmagic, scale, o[4 * j], o[4 * j + 1]);
                         convert_word(w[u][4 * h + 2 * j + 1], zmagic, scale, o[4 * j + 2], o[4 * j + 3]);
                     }
