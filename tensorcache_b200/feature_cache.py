@@ -172,6 +172,7 @@ class FeatureCacheWriter:
         obj = cls.__new__(cls)
         kw = dict(group_size=32, adaptive=False, amo_bq=False, amo_lo=0.95, amo_hi=1.05, amo_candidates=32, amo_mode=None,
                   quant_bits=8)
+        settings.pop("prefault", None)    # a writer-only switch: accepted so that both calls can share one settings dict
         unknown = set(settings) - set(kw)
         if unknown:
             raise TypeError(f"unknown cache setting(s) {sorted(unknown)}")
