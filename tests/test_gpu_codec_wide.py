@@ -128,6 +128,35 @@ def test_decode_all_group_sizes_and_alignments_against_oracle(L, dev):
                     ("sym", G, n, q_off, out_off)
 
 
+def test_decode_with_scales_and_zero_points_at_odd_addresses(L, dev):
+    """The G = 8 / 24 / 48 kernels fetch several scales / zero points per load when the arrays allow it; views that start
+    one element into a larger tensor (2-byte aligned scales, 1-byte aligned zero points) take the scalar loads instead.
+    Same bits either way, codes and output on the 32-byte aligned fast path."""
+    from oracle import amo_oracle as orc
+
+    rng = np.random.default_rng(16)
+    for G in (8, 24, 48, 16, 32):
+        n = 96 * 4099       # a multiple of every group size in the loop
+        ng = n // G
+        q = rng.integers(0, 256, n, dtype=np.uint8)
+        zp = rng.integers(0, 256, ng, dtype=np.uint8)
+        s = bits(torch.exp(torch.rand(ng) * 12 - 9).to(torch.bfloat16))
+        want, want_sym = orc.decompress(q, s, zp, G), orc.decompress_sym(q.view(np.int8), s, G)
+        qd = torch.from_numpy(q).to(dev)
+        for s_off, z_off in ((0, 0), (1, 1), (3, 2), (2, 3)):
+            sd = torch.zeros(ng + 8, dtype=torch.int16, device=dev)
+            sd[s_off:s_off + ng] = torch.from_numpy(s.view(np.int16)).to(dev)
+            zd = torch.zeros(ng + 8, dtype=torch.uint8, device=dev)
+            zd[z_off:z_off + ng] = torch.from_numpy(zp).to(dev)
+            od = torch.empty(n, dtype=torch.int16, device=dev)
+            rc = L.tcb_decompress_amo(qd.data_ptr(), sd.data_ptr() + 2 * s_off, zd.data_ptr() + z_off, od.data_ptr(), n, G, _stream(dev))
+            assert rc == 0, L.tcb_last_error()
+            assert np.array_equal(od.cpu().numpy().view(np.uint16), want), (G, s_off, z_off)
+            rc = L.tcb_decompress_sym(qd.data_ptr(), sd.data_ptr() + 2 * s_off, od.data_ptr(), n, G, _stream(dev))
+            assert rc == 0, L.tcb_last_error()
+            assert np.array_equal(od.cpu().numpy().view(np.uint16), want_sym), ("sym", G, s_off)
+
+
 def test_symmetric_decode_every_code_is_exact(L, dev):
     from oracle import amo_oracle as orc
 
