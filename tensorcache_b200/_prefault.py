@@ -54,7 +54,14 @@ def in_memory_filesystem(path: str) -> bool:
 
 
 def prefault_threads() -> int:
-    """Half of this process's share of the cores, at most 8 (the row copies need the other half)."""
+    """Half of this process's share of the cores, at most 8 (the row copies need the other half);
+    ``TCB_PREFAULT_THREADS`` overrides it."""
+    try:
+        forced = int(os.environ.get("TCB_PREFAULT_THREADS", "0"))
+    except ValueError:
+        forced = 0
+    if forced > 0:
+        return min(forced, 64)
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
         local_ranks = int(os.environ.get("LOCAL_WORLD_SIZE") or os.environ.get("WORLD_SIZE") or 1)
