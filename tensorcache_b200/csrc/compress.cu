@@ -1,19 +1,22 @@
 // AMO-BQ encode kernels for sm_100a: per-group asymmetric min/max plus the scale
 // search of the reference's CPU path, reproduced bit for bit.
 //
-// Two families of kernels share the arithmetic:
+// Three layouts of a group over the lanes share the arithmetic:
 //   * "lane" kernels (compress_legacy_lane_kernel, compress_quality_lane_kernel,
 //     compress_sym_lane_kernel) -- the hot path for G <= 32, and for G = 48 / 64 with
 //     the candidate-table presets: ONE group per lane.  The group's values stay in the
 //     thread's registers, nothing crosses lanes, the per-candidate set-up (scale, zero
 //     point, reciprocal) is paid once per G values, and the squared-error sum follows
 //     the reference's order with plain additions in the right sequence.
-//   * "quad" kernels (compress_legacy_kernel, compress_quality_kernel, compress_sym_kernel)
-//     -- G = 128, and G = 48 / 64 in quality mode, where a group does not fit one thread's
-//     registers: four lanes per group.  Lane j of the quad owns columns 2j and 2j+1 of
-//     every 8-wide vector of the group, so that each lane accumulates its two columns
-//     privately in the reference's order and the four lanes chain their totals with warp
-//     shuffles; min/max use xor-shuffles inside the quad.
+//   * compress_legacy_pair_kernel -- G = 128 with the candidate-table presets: two lanes
+//     per group, lane j owns columns 4j .. 4j+3 of every 8-wide vector, 64 values in
+//     registers each; two shuffles per candidate chain the column totals in order.
+//   * "quad" kernels (compress_quality_kernel, compress_sym_kernel) -- the quality search
+//     at G = 48 / 64 / 128 and the symmetric search at G = 128, where half a group does not
+//     fit one thread's registers either: four lanes per group.  Lane j of the quad owns
+//     columns 2j and 2j+1 of every 8-wide vector of the group, so that each lane
+//     accumulates its two columns privately in the reference's order and the four lanes
+//     chain their totals with warp shuffles; min/max use xor-shuffles inside the quad.
 //   * compress_sym_stream_kernel: the plain symmetric codec has no search and is
 //     HBM-bound; 16 values per thread, one 256-bit load, one 128-bit store.
 // The reference's order of the sum (its CPU reduction): vectors of 8 lanes, four partial
@@ -27,10 +30,10 @@
 //   multipliers are the host's torch.linspace values passed in by value.
 // The kernels are ALU-bound (~14 thread instructions per value and candidate).
 // The reference's per-value IEEE division x / s is computed as the exact IEEE quotient
-// from the candidate's reciprocal and two FMAs (exact_quotient; the lane kernels and the
-// quality search), or as a reciprocal multiply plus a guard that falls back to the real
-// division in the rare case where the two could round to different codes (quant_index;
-// the quad kernels' table presets), so the result is still the reference's, bit for bit.
+// from the candidate's reciprocal and two FMAs (exact_quotient; the lane and pair kernels
+// and the quality search), or as a reciprocal multiply plus a guard that falls back to the
+// real division in the rare case where the two could round to different codes (quant_index;
+// the symmetric quad kernel), so the result is still the reference's, bit for bit.
 // The kernels never synchronise with the host.
 #include <atomic>
 
@@ -183,96 +186,6 @@ __device__ __forceinline__ void store_codes(uint8_t* __restrict__ q, int64_t num
         } else {
             if (i < numel) q[i] = c[2 * k];
             if (i + 1 < numel) q[i + 1] = c[2 * k + 1];
-        }
-    }
-}
-
-// ---------------------------------------------------------------- legacy presets
-
-template <int G, typename T>
-__global__ void __launch_bounds__(kThreads)
-compress_legacy_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
-                       uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned, bool out_aligned) {
-    constexpr int VPL = G / 4;
-    constexpr uint32_t kAllFinite = VPL >= 32 ? 0xffffffffu : (1u << (VPL & 31)) - 1u;
-    const int lane = threadIdx.x & 31;
-    const int j = lane & 3;
-    const uint32_t qmask = 0xFu << (lane & ~3);
-    const int64_t quads_per_grid = int64_t(gridDim.x) * (kThreads / 4);
-
-    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 4) + (threadIdx.x >> 2); g < ngroups; g += quads_per_grid) {
-        const int64_t base = g * G;
-        float v[VPL];
-        uint32_t finmask;
-        load_lane<G, T>(x, numel, base, j, in_aligned, v, finmask);
-
-        float lmin = v[0], lmax = v[0];
-#pragma unroll
-        for (int k = 1; k < VPL; ++k) {
-            lmin = fminf(lmin, v[k]);
-            lmax = fmaxf(lmax, v[k]);
-        }
-        const float bmin = quad_min(lmin, qmask);
-        const float bmax = quad_max(lmax, qmask);
-        float rng = fmaxf(__fsub_rn(bmax, bmin), 1e-8f);
-        if (!finite_f32(rng)) rng = 1e-8f;
-        float s0 = __fdiv_rn(rng, 255.0f);
-        if (!finite_f32(s0)) s0 = float(1e-8 / 255.0);
-        const float nbmin = -bmin;
-
-        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
-        for (int c = 0; c < tab.n; ++c) {
-            const float s = __fmul_rn(s0, tab.m[c]);
-            const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
-            const float rcp = __frcp_rn(s);
-            // Straight-line fast path for all of the lane's values (see quant_index for why it is exact
-            // away from rounding boundaries); the rare values that sit on a boundary are redone with the
-            // IEEE division afterwards, so the common case carries no per-value branch.
-            float e[VPL], kq[VPL];
-            bool doubtful = false;
-#pragma unroll
-            for (int k = 0; k < VPL; ++k) {
-                const float t = __fmaf_rn(v[k], rcp, zp);  // one rounding fewer than the bound in quant_index assumes
-                kq[k] = rintf(t);
-                doubtful |= !(fabsf(__fsub_rn(t, kq[k])) <= kBoundaryGuard);
-            }
-            if (doubtful) {
-#pragma unroll
-                for (int k = 0; k < VPL; ++k) kq[k] = quant_index(v[k], s, rcp, zp);
-            }
-#pragma unroll
-            for (int k = 0; k < VPL; ++k) {
-                const float qc = clamp255(kq[k]);
-                const float rec = __fmul_rn(__fsub_rn(qc, zp), s);
-                const float d = __fsub_rn(v[k], rec);
-                e[k] = __fmul_rn(d, d);
-            }
-            if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
-#pragma unroll
-                for (int k = 0; k < VPL; ++k)
-                    if (!((finmask >> k) & 1u)) e[k] = 0.0f;
-            }
-            const float err = quad_sum<G>(e, j, lane, qmask);
-            if (c == 0 || err < best_err) {
-                best_err = err;
-                best_s = s;
-                best_zp = zp;
-            }
-        }
-
-        uint8_t codes[VPL];
-        const uint8_t zp8 = uint8_t(best_zp);
-#pragma unroll
-        for (int k = 0; k < VPL; ++k) {
-            const float t = __fadd_rn(__fdiv_rn(v[k], best_s), best_zp);
-            const float qf = clamp255(rintf(t));
-            codes[k] = ((finmask >> k) & 1u) ? uint8_t(qf) : zp8;
-        }
-        store_codes<G>(q, numel, base, j, out_aligned, codes);
-        if (j == 0) {
-            __nv_bfloat16 sb = __float2bfloat16_rn(best_s);
-            scales[g] = *reinterpret_cast<uint16_t*>(&sb);
-            zps[g] = zp8;
         }
     }
 }
@@ -575,6 +488,136 @@ compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
         store_group<G>(q, numel, base, out_aligned8, cw);
         scales[g] = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
         zps[g] = uint8_t(zp8);
+    }
+}
+
+// ------------------------------------------------- two lanes per group (G = 128, legacy presets)
+//
+// 128 values do not fit one thread, but 64 do: lane j (0 / 1) of a pair owns columns 4 j .. 4 j + 3 of every 8-wide
+// vector of the group.  Every running sum of the reference (accumulator v % 4 of column l, see LaneSums) then lives in
+// one lane, the column totals are chained left to right through ONE shuffle (lane 0's partial total is lane 1's
+// starting value), and a second shuffle hands the group's total back.  Everything else is the one-lane kernel: the
+// exact two-FMA quotient, the same rare fall-backs, 64 values in registers.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                            uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned8, bool out_aligned4) {
+    constexpr int G = 128, NV = G / 8;          // 16 vectors of 8; this lane holds 4 values of each
+    const int lane = threadIdx.x & 31, j = lane & 1;
+    const uint32_t pmask = 3u << (lane & ~1);
+    const int64_t pairs_per_grid = int64_t(gridDim.x) * (kThreads / 2);
+    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
+        const int64_t base = g * G + 4 * j;      // this lane's values: base + 8 v + i, v < 16, i < 4
+        float v[64];
+        if (g * G + G <= numel && in_aligned8) {
+#pragma unroll
+            for (int vI = 0; vI < NV; ++vI) {
+                if (sizeof(T) == 4) {
+                    const uint4 w = __ldg(reinterpret_cast<const uint4*>(x + base + 8 * vI));
+                    v[4 * vI] = __uint_as_float(w.x), v[4 * vI + 1] = __uint_as_float(w.y);
+                    v[4 * vI + 2] = __uint_as_float(w.z), v[4 * vI + 3] = __uint_as_float(w.w);
+                } else {
+                    const uint2 w = __ldg(reinterpret_cast<const uint2*>(x + base + 8 * vI));
+                    uint16_t h0 = uint16_t(w.x), h1 = uint16_t(w.x >> 16), h2 = uint16_t(w.y), h3 = uint16_t(w.y >> 16);
+                    v[4 * vI] = widen<T>(*reinterpret_cast<T*>(&h0)), v[4 * vI + 1] = widen<T>(*reinterpret_cast<T*>(&h1));
+                    v[4 * vI + 2] = widen<T>(*reinterpret_cast<T*>(&h2)), v[4 * vI + 3] = widen<T>(*reinterpret_cast<T*>(&h3));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 64; ++k) {
+                const int64_t at = base + 8 * (k >> 2) + (k & 3);
+                v[k] = at < numel ? widen<T>(x[at]) : 0.0f;
+            }
+        }
+        uint64_t finmask = 0;
+#pragma unroll
+        for (int k = 0; k < 64; ++k) {
+            const bool f = finite_f32(v[k]);
+            if (!f) v[k] = 0.0f;
+            finmask |= uint64_t(f ? 1 : 0) << k;
+        }
+        float bmin = v[0], bmax = v[0];
+#pragma unroll
+        for (int k = 1; k < 64; ++k) {
+            bmin = fminf(bmin, v[k]);
+            bmax = fmaxf(bmax, v[k]);
+        }
+        bmin = fminf(bmin, __shfl_xor_sync(pmask, bmin, 1));
+        bmax = fmaxf(bmax, __shfl_xor_sync(pmask, bmax, 1));
+        const bool all_finite = __all_sync(pmask, finmask == ~uint64_t(0));
+        float rng = fmaxf(__fsub_rn(bmax, bmin), 1e-8f);
+        if (!finite_f32(rng)) rng = 1e-8f;
+        float s0 = __fdiv_rn(rng, 255.0f);
+        if (!finite_f32(s0)) s0 = float(1e-8 / 255.0);
+        const float nbmin = -bmin;
+        const float amax = fmaxf(fabsf(bmin), fabsf(bmax));
+
+        float best_err = 0.0f, best_s = 0.0f, best_zp = 0.0f;
+        for (int c = 0; c < tab.n; ++c) {
+            const float s = __fmul_rn(s0, tab.m[c]);
+            const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
+            const float rcp = __frcp_rn(s);
+            float acc[4][4];                    // [accumulator v % 4][column of this lane]
+            const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu && __fmul_rn(amax, rcp) < 1048576.0f && all_finite;
+            if (plain) {
+#pragma unroll
+                for (int k = 0; k < 64; ++k) {
+                    const float qc = clamp255(rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
+                    const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
+                    const float e = __fmul_rn(d, d);
+                    const int vI = k >> 2, l = k & 3;
+                    acc[vI & 3][l] = vI < 4 ? e : __fadd_rn(acc[vI & 3][l], e);
+                }
+            } else {  // rare: divide, and leave out the positions that held NaN / Inf
+#pragma unroll
+                for (int k = 0; k < 64; ++k) {
+                    const float qc = clamp255(rintf(__fadd_rn(__fdiv_rn(v[k], s), zp)));
+                    const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
+                    const float e = ((finmask >> k) & 1u) ? __fmul_rn(d, d) : 0.0f;
+                    const int vI = k >> 2, l = k & 3;
+                    acc[vI & 3][l] = vI < 4 ? e : __fadd_rn(acc[vI & 3][l], e);
+                }
+            }
+            float lt[4];
+#pragma unroll
+            for (int l = 0; l < 4; ++l) lt[l] = __fadd_rn(__fadd_rn(__fadd_rn(acc[0][l], acc[1][l]), acc[2][l]), acc[3][l]);
+            // columns 0..3 (lane 0), then 4..7 (lane 1), left to right
+            const float left = __fadd_rn(__fadd_rn(__fadd_rn(lt[0], lt[1]), lt[2]), lt[3]);
+            const float carried = __shfl_sync(pmask, left, lane & ~1);
+            const float right = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(carried, lt[0]), lt[1]), lt[2]), lt[3]);
+            const float err = __shfl_sync(pmask, right, lane | 1);
+            if (c == 0 || err < best_err) {
+                best_err = err;
+                best_s = s;
+                best_zp = zp;
+            }
+        }
+
+        const uint32_t zp8 = uint32_t(best_zp);
+        const bool whole = g * G + G <= numel && out_aligned4;
+#pragma unroll
+        for (int vI = 0; vI < NV; ++vI) {
+            uint32_t cw = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = 4 * vI + i;
+                const float qf = clamp255(rintf(__fadd_rn(__fdiv_rn(v[k], best_s), best_zp)));
+                const uint32_t code = ((finmask >> k) & 1u) ? uint32_t(qf) : zp8;
+                cw |= code << (8 * i);
+            }
+            if (whole) {
+                *reinterpret_cast<uint32_t*>(q + base + 8 * vI) = cw;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (base + 8 * vI + i < numel) q[base + 8 * vI + i] = uint8_t(cw >> (8 * i));
+            }
+        }
+        if (j == 0) {
+            scales[g] = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
+            zps[g] = uint8_t(zp8);
+        }
     }
 }
 
@@ -1003,7 +1046,12 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
             const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
             compress_legacy_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in16, out8);
         } else {
-            compress_legacy_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in_aligned, out_aligned);
+            static_assert(G == 128, "the two-lanes-per-group kernel is written for G = 128");
+            const bool in8 = reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T)) == 0;
+            const bool out4 = reinterpret_cast<uintptr_t>(q) % 4 == 0;
+            const int64_t blocks = (ngroups + kThreads / 2 - 1) / (kThreads / 2);
+            const int pair_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
+            compress_legacy_pair_kernel<T><<<pair_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in8, out4);
         }
         break;
     case Coder::Quality:
