@@ -8,12 +8,13 @@
 //     thread's registers, nothing crosses lanes, the per-candidate set-up (scale, zero
 //     point, reciprocal) is paid once per G values, and the squared-error sum follows
 //     the reference's order with plain additions in the right sequence.
-//   * compress_legacy_pair_kernel -- G = 128 with the candidate-table presets: two lanes
-//     per group, lane j owns columns 4j .. 4j+3 of every 8-wide vector, 64 values in
-//     registers each; two shuffles per candidate chain the column totals in order.
-//   * "quad" kernels (compress_quality_kernel, compress_sym_kernel) -- the quality search
-//     at G = 48 / 64 / 128 and the symmetric search at G = 128, where half a group does not
-//     fit one thread's registers either: four lanes per group.  Lane j of the quad owns
+//   * "pair" kernels (compress_legacy_pair_kernel, compress_sym_pair_kernel) -- G = 128
+//     with the candidate-table presets and the symmetric search: two lanes per group,
+//     lane j owns columns 4j .. 4j+3 of every 8-wide vector, 64 values in registers
+//     each; two shuffles per candidate chain the column totals in order.
+//   * the "quad" kernel (compress_quality_kernel) -- the quality search at G = 48 / 64 /
+//     128, where its three code trials per value leave no room for 64 values in one
+//     thread's registers: four lanes per group.  Lane j of the quad owns
 //     columns 2j and 2j+1 of every 8-wide vector of the group, so that each lane
 //     accumulates its two columns privately in the reference's order and the four lanes
 //     chain their totals with warp shuffles; min/max use xor-shuffles inside the quad.
@@ -30,10 +31,8 @@
 //   multipliers are the host's torch.linspace values passed in by value.
 // The kernels are ALU-bound (~14 thread instructions per value and candidate).
 // The reference's per-value IEEE division x / s is computed as the exact IEEE quotient
-// from the candidate's reciprocal and two FMAs (exact_quotient; the lane and pair kernels
-// and the quality search), or as a reciprocal multiply plus a guard that falls back to the
-// real division in the rare case where the two could round to different codes (quant_index;
-// the symmetric quad kernel), so the result is still the reference's, bit for bit.
+// from the candidate's reciprocal and two FMAs (exact_quotient), so the result is still the
+// reference's, bit for bit.
 // The kernels never synchronise with the host.
 #include <atomic>
 
@@ -55,32 +54,14 @@ __device__ __forceinline__ bool finite_f32(float v) { return (__float_as_uint(v)
 
 __device__ __forceinline__ float clamp255(float v) { return fminf(fmaxf(v, 0.0f), 255.0f); }
 
-// rint(x / s + zp) with the IEEE quotient, without paying for an IEEE division per value.
-// `r` is the correctly rounded reciprocal of s (one per candidate).  t~ = x * r + zp differs from
-// the reference's t = fl(fl(x / s) + zp) by less than 2^-13 whenever |t~| < 512 (the product is
-// within 2.5 ulp of the quotient, ulp <= 2^-15 there, plus one rounding of the sum on each side),
-// so both round to the same integer unless t~ lies within 2^-12 of a half-integer; only then is the
-// exact division evaluated.  For |t~| >= 512 the two values may differ by more, but both are far
-// outside [0, 255] on the same side and clamp identically whichever path is taken.  NaN (never
-// produced for finite inputs) takes the exact path.
-constexpr float kBoundaryGuard = 0.5f - 0x1p-12f;  // distance from the nearest integer up to which the fast path is trusted
-
-__device__ __forceinline__ float quant_index(float x, float s, float r, float zp) {
-    const float t = __fadd_rn(__fmul_rn(x, r), zp);
-    float k = rintf(t);
-    const float dist = fabsf(__fsub_rn(t, k));
-    if (!(dist <= kBoundaryGuard)) k = rintf(__fadd_rn(__fdiv_rn(x, s), zp));
-    return k;
-}
-
 // The correctly rounded quotient x / s without a division, for a divisor whose significand is not
 // all ones (the scales of the quality search and of the symmetric codec are bf16 values: 8 bits).
 // With r = rn(1 / s) and t = rn(x * r), the residual x - t * s is exact in one FMA and
 // rn(t + residual * r) is the IEEE quotient (Markstein's correction step, the one a division routine
 // ends with).  The residual can only underflow where the quotient is far below 2^-20, which cannot
-// change the rounded code.  Needed, rather than the guard of quant_index, wherever values and scale
-// are both short: then x / s lands exactly on k + 0.5 for a large share of the values and a
-// "rare boundary" fallback would run all the time.
+// change the rounded code.  A cheaper reciprocal multiply with a fall-back near rounding boundaries does not do
+// here: values and scales are often both short, so x / s lands exactly on k + 0.5 for a large share of the values
+// and the "rare" fall-back would run all the time.
 __device__ __forceinline__ float exact_quotient(float x, float s, float r) {
     const float t = __fmul_rn(x, r);
     return __fmaf_rn(__fmaf_rn(-t, s, x), r, t);
@@ -498,45 +479,87 @@ compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
 // one lane, the column totals are chained left to right through ONE shuffle (lane 0's partial total is lane 1's
 // starting value), and a second shuffle hands the group's total back.  Everything else is the one-lane kernel: the
 // exact two-FMA quotient, the same rare fall-backs, 64 values in registers.
+constexpr int kPairG = 128;   // group size of the two-lanes-per-group kernels
+
+// The 64 values of lane j of a pair: element 8 v + 4 j + i of group g is v[4 v + i].  Non-finite values become 0 and
+// clear their bit in `finmask`.
+template <typename T>
+__device__ __forceinline__ void pair_load(const T* __restrict__ x, int64_t numel, int64_t g, int j, bool aligned, float (&v)[64],
+                                          uint64_t& finmask) {
+    const int64_t base = g * kPairG + 4 * j;
+    if (g * kPairG + kPairG <= numel && aligned) {
+#pragma unroll
+        for (int vI = 0; vI < kPairG / 8; ++vI) {
+            if (sizeof(T) == 4) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(x + base + 8 * vI));
+                v[4 * vI] = __uint_as_float(w.x), v[4 * vI + 1] = __uint_as_float(w.y);
+                v[4 * vI + 2] = __uint_as_float(w.z), v[4 * vI + 3] = __uint_as_float(w.w);
+            } else {
+                const uint2 w = __ldg(reinterpret_cast<const uint2*>(x + base + 8 * vI));
+                uint16_t h0 = uint16_t(w.x), h1 = uint16_t(w.x >> 16), h2 = uint16_t(w.y), h3 = uint16_t(w.y >> 16);
+                v[4 * vI] = widen<T>(*reinterpret_cast<T*>(&h0)), v[4 * vI + 1] = widen<T>(*reinterpret_cast<T*>(&h1));
+                v[4 * vI + 2] = widen<T>(*reinterpret_cast<T*>(&h2)), v[4 * vI + 3] = widen<T>(*reinterpret_cast<T*>(&h3));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 64; ++k) {
+            const int64_t at = base + 8 * (k >> 2) + (k & 3);
+            v[k] = at < numel ? widen<T>(x[at]) : 0.0f;
+        }
+    }
+    finmask = 0;
+#pragma unroll
+    for (int k = 0; k < 64; ++k) {
+        const bool f = finite_f32(v[k]);
+        if (!f) v[k] = 0.0f;
+        finmask |= uint64_t(f ? 1 : 0) << k;
+    }
+}
+
+// The reference's running sums for the four columns this lane owns (LaneSums for G = 128, split by column), and the
+// group's total: columns 0..3 (lane 0) then 4..7 (lane 1), left to right, with lane 0's partial total as lane 1's
+// starting value.  Both lanes of the pair return the same number.
+struct PairSums {
+    float acc[4][4];                    // [accumulator v % 4][column of this lane]
+    __device__ __forceinline__ void add(int k, float e) {
+        const int vI = k >> 2, l = k & 3;
+        acc[vI & 3][l] = vI < 4 ? e : __fadd_rn(acc[vI & 3][l], e);
+    }
+    __device__ __forceinline__ float total(uint32_t pmask, int lane) const {
+        float lt[4];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) lt[l] = __fadd_rn(__fadd_rn(__fadd_rn(acc[0][l], acc[1][l]), acc[2][l]), acc[3][l]);
+        const float left = __fadd_rn(__fadd_rn(__fadd_rn(lt[0], lt[1]), lt[2]), lt[3]);
+        const float carried = __shfl_sync(pmask, left, lane & ~1);
+        const float right = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(carried, lt[0]), lt[1]), lt[2]), lt[3]);
+        return __shfl_sync(pmask, right, lane | 1);
+    }
+};
+
+// the four codes of vector vI that this lane owns
+__device__ __forceinline__ void pair_store(uint8_t* __restrict__ q, int64_t numel, int64_t g, int j, int vI, bool whole, uint32_t cw) {
+    const int64_t at = g * kPairG + 4 * j + 8 * vI;
+    if (whole) {
+        *reinterpret_cast<uint32_t*>(q + at) = cw;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (at + i < numel) q[at + i] = uint8_t(cw >> (8 * i));
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned8, bool out_aligned4) {
-    constexpr int G = 128, NV = G / 8;          // 16 vectors of 8; this lane holds 4 values of each
     const int lane = threadIdx.x & 31, j = lane & 1;
     const uint32_t pmask = 3u << (lane & ~1);
     const int64_t pairs_per_grid = int64_t(gridDim.x) * (kThreads / 2);
     for (int64_t g = int64_t(blockIdx.x) * (kThreads / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
-        const int64_t base = g * G + 4 * j;      // this lane's values: base + 8 v + i, v < 16, i < 4
         float v[64];
-        if (g * G + G <= numel && in_aligned8) {
-#pragma unroll
-            for (int vI = 0; vI < NV; ++vI) {
-                if (sizeof(T) == 4) {
-                    const uint4 w = __ldg(reinterpret_cast<const uint4*>(x + base + 8 * vI));
-                    v[4 * vI] = __uint_as_float(w.x), v[4 * vI + 1] = __uint_as_float(w.y);
-                    v[4 * vI + 2] = __uint_as_float(w.z), v[4 * vI + 3] = __uint_as_float(w.w);
-                } else {
-                    const uint2 w = __ldg(reinterpret_cast<const uint2*>(x + base + 8 * vI));
-                    uint16_t h0 = uint16_t(w.x), h1 = uint16_t(w.x >> 16), h2 = uint16_t(w.y), h3 = uint16_t(w.y >> 16);
-                    v[4 * vI] = widen<T>(*reinterpret_cast<T*>(&h0)), v[4 * vI + 1] = widen<T>(*reinterpret_cast<T*>(&h1));
-                    v[4 * vI + 2] = widen<T>(*reinterpret_cast<T*>(&h2)), v[4 * vI + 3] = widen<T>(*reinterpret_cast<T*>(&h3));
-                }
-            }
-        } else {
-#pragma unroll
-            for (int k = 0; k < 64; ++k) {
-                const int64_t at = base + 8 * (k >> 2) + (k & 3);
-                v[k] = at < numel ? widen<T>(x[at]) : 0.0f;
-            }
-        }
-        uint64_t finmask = 0;
-#pragma unroll
-        for (int k = 0; k < 64; ++k) {
-            const bool f = finite_f32(v[k]);
-            if (!f) v[k] = 0.0f;
-            finmask |= uint64_t(f ? 1 : 0) << k;
-        }
+        uint64_t finmask;
+        pair_load<T>(x, numel, g, j, in_aligned8, v, finmask);
         float bmin = v[0], bmax = v[0];
 #pragma unroll
         for (int k = 1; k < 64; ++k) {
@@ -558,35 +581,24 @@ compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
             const float s = __fmul_rn(s0, tab.m[c]);
             const float zp = clamp255(rintf(__fdiv_rn(nbmin, s)));
             const float rcp = __frcp_rn(s);
-            float acc[4][4];                    // [accumulator v % 4][column of this lane]
+            PairSums sums;
             const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu && __fmul_rn(amax, rcp) < 1048576.0f && all_finite;
             if (plain) {
 #pragma unroll
                 for (int k = 0; k < 64; ++k) {
                     const float qc = clamp255(rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
                     const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
-                    const float e = __fmul_rn(d, d);
-                    const int vI = k >> 2, l = k & 3;
-                    acc[vI & 3][l] = vI < 4 ? e : __fadd_rn(acc[vI & 3][l], e);
+                    sums.add(k, __fmul_rn(d, d));
                 }
             } else {  // rare: divide, and leave out the positions that held NaN / Inf
 #pragma unroll
                 for (int k = 0; k < 64; ++k) {
                     const float qc = clamp255(rintf(__fadd_rn(__fdiv_rn(v[k], s), zp)));
                     const float d = __fsub_rn(v[k], __fmul_rn(__fsub_rn(qc, zp), s));
-                    const float e = ((finmask >> k) & 1u) ? __fmul_rn(d, d) : 0.0f;
-                    const int vI = k >> 2, l = k & 3;
-                    acc[vI & 3][l] = vI < 4 ? e : __fadd_rn(acc[vI & 3][l], e);
+                    sums.add(k, ((finmask >> k) & 1u) ? __fmul_rn(d, d) : 0.0f);
                 }
             }
-            float lt[4];
-#pragma unroll
-            for (int l = 0; l < 4; ++l) lt[l] = __fadd_rn(__fadd_rn(__fadd_rn(acc[0][l], acc[1][l]), acc[2][l]), acc[3][l]);
-            // columns 0..3 (lane 0), then 4..7 (lane 1), left to right
-            const float left = __fadd_rn(__fadd_rn(__fadd_rn(lt[0], lt[1]), lt[2]), lt[3]);
-            const float carried = __shfl_sync(pmask, left, lane & ~1);
-            const float right = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(carried, lt[0]), lt[1]), lt[2]), lt[3]);
-            const float err = __shfl_sync(pmask, right, lane | 1);
+            const float err = sums.total(pmask, lane);
             if (c == 0 || err < best_err) {
                 best_err = err;
                 best_s = s;
@@ -595,9 +607,9 @@ compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
         }
 
         const uint32_t zp8 = uint32_t(best_zp);
-        const bool whole = g * G + G <= numel && out_aligned4;
+        const bool whole = g * kPairG + kPairG <= numel && out_aligned4;
 #pragma unroll
-        for (int vI = 0; vI < NV; ++vI) {
+        for (int vI = 0; vI < kPairG / 8; ++vI) {
             uint32_t cw = 0;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -606,13 +618,7 @@ compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
                 const uint32_t code = ((finmask >> k) & 1u) ? uint32_t(qf) : zp8;
                 cw |= code << (8 * i);
             }
-            if (whole) {
-                *reinterpret_cast<uint32_t*>(q + base + 8 * vI) = cw;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (base + 8 * vI + i < numel) q[base + 8 * vI + i] = uint8_t(cw >> (8 * i));
-            }
+            pair_store(q, numel, g, j, vI, whole, cw);
         }
         if (j == 0) {
             scales[g] = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
@@ -702,72 +708,12 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
 
 __device__ __forceinline__ float clamp_i8(float v) { return fminf(fmaxf(v, -128.0f), 127.0f); }
 
-// src/tensorcache/codec.py:530-565 (tab.n == 0: scale = bf16(max|x| / 127)) and :568-620 (tab.n > 0: the
-// "adaptive" search over s0 * multiplier, scored on the raw values so that a NaN / Inf in the group
-// makes every score NaN / Inf and candidate 0 wins, then the winner rounded to bf16).  Signed codes.
-template <int G, typename T>
-__global__ void __launch_bounds__(kThreads)
-compress_sym_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
-                    uint16_t* __restrict__ scales, bool in_aligned, bool out_aligned) {
-    constexpr int VPL = G / 4;
-    constexpr uint32_t kAllFinite = VPL >= 32 ? 0xffffffffu : (1u << (VPL & 31)) - 1u;
-    const int lane = threadIdx.x & 31;
-    const int j = lane & 3;
-    const uint32_t qmask = 0xFu << (lane & ~3);
-    const int64_t quads_per_grid = int64_t(gridDim.x) * (kThreads / 4);
-
-    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 4) + (threadIdx.x >> 2); g < ngroups; g += quads_per_grid) {
-        const int64_t base = g * G;
-        float v[VPL];
-        uint32_t finmask;
-        load_lane<G, T>(x, numel, base, j, in_aligned, v, finmask);
-
-        float lmax = fabsf(v[0]);
-#pragma unroll
-        for (int k = 1; k < VPL; ++k) lmax = fmaxf(lmax, fabsf(v[k]));
-        const float bmax = fmaxf(quad_max(lmax, qmask), 1e-8f);
-        const float s0 = __fdiv_rn(bmax, 127.0f);
-
-        float best_s = s0;
-        if (tab.n > 0) {
-            // a group that held a non-finite value scores NaN or +Inf under every candidate: candidate 0 wins
-            const bool all_finite = __all_sync(qmask, finmask == kAllFinite);
-            best_s = __fmul_rn(s0, tab.m[0]);
-            if (all_finite) {
-                float best_err = 0.0f;
-                for (int c = 0; c < tab.n; ++c) {
-                    const float s = __fmul_rn(s0, tab.m[c]);
-                    const float rcp = __frcp_rn(s);
-                    float e[VPL];
-#pragma unroll
-                    for (int k = 0; k < VPL; ++k) {
-                        const float qc = clamp_i8(quant_index(v[k], s, rcp, 0.0f));
-                        const float d = __fsub_rn(v[k], __fmul_rn(qc, s));
-                        e[k] = __fmul_rn(d, d);
-                    }
-                    const float err = quad_sum<G>(e, j, lane, qmask);
-                    if (c == 0 || err < best_err) {
-                        best_err = err;
-                        best_s = s;
-                    }
-                }
-            }
-        }
-        const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
-        const float sf = __uint_as_float(uint32_t(sbits) << 16);
-        uint8_t codes[VPL];
-#pragma unroll
-        for (int k = 0; k < VPL; ++k) {
-            const float qf = clamp_i8(rintf(__fdiv_rn(v[k], sf)));
-            codes[k] = ((finmask >> k) & 1u) ? uint8_t(int8_t(int(qf))) : uint8_t(0);
-        }
-        store_codes<G>(q, numel, base, j, out_aligned, codes);
-        if (j == 0) scales[g] = sbits;
-    }
-}
 
 // The adaptive search of the symmetric codec with one group per lane (G <= 32), like the AMO-BQ lane kernels.
 // |x| <= max|x| and every candidate scale is at least 0.9 max|x| / 127, so the quotients stay below 142.
+// src/tensorcache/codec.py:530-565 (tab.n == 0: scale = bf16(max|x| / 127)) and :568-620 (tab.n > 0: the
+// "adaptive" search over s0 * multiplier, scored on the raw values so that a NaN / Inf in the group
+// makes every score NaN / Inf and candidate 0 wins, then the winner rounded to bf16).  Signed codes.
 template <int G, typename T>
 __global__ void __launch_bounds__(kThreads)
 compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
@@ -827,6 +773,75 @@ compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups
         }
         store_group<G>(q, numel, base, out_aligned8, cw);
         scales[g] = sbits;
+    }
+}
+
+// The same search with two lanes per group (G = 128): the layout of compress_legacy_pair_kernel, the arithmetic of
+// compress_sym_lane_kernel.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+compress_sym_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups, CandTable tab, uint8_t* __restrict__ q,
+                         uint16_t* __restrict__ scales, bool in_aligned8, bool out_aligned4) {
+    const int lane = threadIdx.x & 31, j = lane & 1;
+    const uint32_t pmask = 3u << (lane & ~1);
+    const int64_t pairs_per_grid = int64_t(gridDim.x) * (kThreads / 2);
+    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
+        float v[64];
+        uint64_t finmask;
+        pair_load<T>(x, numel, g, j, in_aligned8, v, finmask);
+        float amax = fabsf(v[0]);
+#pragma unroll
+        for (int k = 1; k < 64; ++k) amax = fmaxf(amax, fabsf(v[k]));
+        amax = fmaxf(amax, __shfl_xor_sync(pmask, amax, 1));
+        const bool all_finite = __all_sync(pmask, finmask == ~uint64_t(0));
+        const float s0 = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        float best_s = s0;
+        if (tab.n > 0) {
+            best_s = __fmul_rn(s0, tab.m[0]);  // a group that held NaN / Inf scores NaN / Inf everywhere: candidate 0
+            if (all_finite) {
+                float best_err = 0.0f;
+                for (int c = 0; c < tab.n; ++c) {
+                    const float s = __fmul_rn(s0, tab.m[c]);
+                    const float rcp = __frcp_rn(s);
+                    const bool plain = (__float_as_uint(s) & 0x7fffffu) != 0x7fffffu;
+                    PairSums sums;
+                    if (plain) {
+#pragma unroll
+                        for (int k = 0; k < 64; ++k) {
+                            const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(exact_quotient(v[k], s, rcp))), s));
+                            sums.add(k, __fmul_rn(d, d));
+                        }
+                    } else {  // rare: a scale whose significand is all ones takes the division
+#pragma unroll
+                        for (int k = 0; k < 64; ++k) {
+                            const float d = __fsub_rn(v[k], __fmul_rn(clamp_i8(rintf(__fdiv_rn(v[k], s))), s));
+                            sums.add(k, __fmul_rn(d, d));
+                        }
+                    }
+                    const float err = sums.total(pmask, lane);
+                    if (c == 0 || err < best_err) {
+                        best_err = err;
+                        best_s = s;
+                    }
+                }
+            }
+        }
+        const uint16_t sbits = __bfloat16_as_ushort(__float2bfloat16_rn(best_s));
+        const float sf = __uint_as_float(uint32_t(sbits) << 16);
+        const bool whole = g * kPairG + kPairG <= numel && out_aligned4;
+#pragma unroll
+        for (int vI = 0; vI < kPairG / 8; ++vI) {
+            uint32_t cw = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = 4 * vI + i;
+                const float qf = clamp_i8(rintf(__fdiv_rn(v[k], sf)));
+                const uint32_t code = ((finmask >> k) & 1u) ? (uint32_t(int(qf)) & 0xffu) : 0u;
+                cw |= code << (8 * i);
+            }
+            pair_store(q, numel, g, j, vI, whole, cw);
+        }
+        if (j == 0) scales[g] = sbits;
     }
 }
 
@@ -1073,7 +1088,12 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
             const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
             compress_sym_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in16, out8);
         } else {
-            compress_sym_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in_aligned, out_aligned);
+            static_assert(G == 128, "the two-lanes-per-group kernel is written for G = 128");
+            const bool in8 = reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T)) == 0;
+            const bool out4 = reinterpret_cast<uintptr_t>(q) % 4 == 0;
+            const int64_t blocks = (ngroups + kThreads / 2 - 1) / (kThreads / 2);
+            const int pair_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
+            compress_sym_pair_kernel<T><<<pair_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in8, out4);
         }
         break;
     }
