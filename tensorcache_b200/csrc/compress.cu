@@ -407,7 +407,7 @@ compress_legacy_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
     static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
-    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * blockDim.x) {
         const int64_t base = g * G;
         float v[G];
         uint64_t finmask;
@@ -555,8 +555,8 @@ compress_legacy_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngro
                             uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned8, bool out_aligned4) {
     const int lane = threadIdx.x & 31, j = lane & 1;
     const uint32_t pmask = 3u << (lane & ~1);
-    const int64_t pairs_per_grid = int64_t(gridDim.x) * (kThreads / 2);
-    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
+    const int64_t pairs_per_grid = int64_t(gridDim.x) * (blockDim.x / 2);
+    for (int64_t g = int64_t(blockIdx.x) * (blockDim.x / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
         float v[64];
         uint64_t finmask;
         pair_load<T>(x, numel, g, j, in_aligned8, v, finmask);
@@ -633,7 +633,7 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
                              uint16_t* __restrict__ scales, uint8_t* __restrict__ zps, bool in_aligned16, bool out_aligned8) {
     static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
-    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * blockDim.x) {
         const int64_t base = g * G;
         float v[G];
         uint64_t finmask;
@@ -720,7 +720,7 @@ compress_sym_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups
                          uint16_t* __restrict__ scales, bool in_aligned16, bool out_aligned8) {
     static_assert(G == 8 || G == 16 || G == 24 || G == 32 || G == 48 || G == 64, "group sizes with a one-group-per-lane kernel");
     constexpr uint64_t kAllFinite = GroupMask<G>::kAll;
-    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * kThreads) {
+    for (int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < ngroups; g += int64_t(gridDim.x) * blockDim.x) {
         const int64_t base = g * G;
         float v[G];
         uint64_t finmask;
@@ -784,8 +784,8 @@ compress_sym_pair_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups
                          uint16_t* __restrict__ scales, bool in_aligned8, bool out_aligned4) {
     const int lane = threadIdx.x & 31, j = lane & 1;
     const uint32_t pmask = 3u << (lane & ~1);
-    const int64_t pairs_per_grid = int64_t(gridDim.x) * (kThreads / 2);
-    for (int64_t g = int64_t(blockIdx.x) * (kThreads / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
+    const int64_t pairs_per_grid = int64_t(gridDim.x) * (blockDim.x / 2);
+    for (int64_t g = int64_t(blockIdx.x) * (blockDim.x / 2) + (threadIdx.x >> 1); g < ngroups; g += pairs_per_grid) {
         float v[64];
         uint64_t finmask;
         pair_load<T>(x, numel, g, j, in_aligned8, v, finmask);
@@ -1052,30 +1052,32 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
     const T* xt = static_cast<const T*>(x);
     const bool in_aligned = (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0;
     const bool out_aligned = (reinterpret_cast<uintptr_t>(q) & 1) == 0;
+    // Kernels that hold 48 or more values per thread need about 180 registers: blocks of 64 threads let an SM hold ten
+    // warps of them where one block of 256 would leave it with eight.
+    constexpr int kLaneThreads = G >= 48 ? 64 : kThreads;
+    auto blocks_for = [&](int groups_per_block) {
+        const int64_t blocks = (ngroups + groups_per_block - 1) / groups_per_block;
+        const int64_t cap = int64_t(grid) * (kThreads / kLaneThreads);
+        return int(blocks < cap ? blocks : cap);
+    };
     switch (coder) {
     case Coder::Legacy:
         if constexpr (G <= 64) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
-            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
-            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
-            compress_legacy_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in16, out8);
+            compress_legacy_lane_kernel<G, T><<<blocks_for(kLaneThreads), kLaneThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in16, out8);
         } else {
             static_assert(G == 128, "the two-lanes-per-group kernel is written for G = 128");
             const bool in8 = reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T)) == 0;
             const bool out4 = reinterpret_cast<uintptr_t>(q) % 4 == 0;
-            const int64_t blocks = (ngroups + kThreads / 2 - 1) / (kThreads / 2);
-            const int pair_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
-            compress_legacy_pair_kernel<T><<<pair_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in8, out4);
+            compress_legacy_pair_kernel<T><<<blocks_for(kLaneThreads / 2), kLaneThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, zp, in8, out4);
         }
         break;
     case Coder::Quality:
         if constexpr (G <= 32) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
-            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
-            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
-            compress_quality_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in16, out8);
+            compress_quality_lane_kernel<G, T><<<blocks_for(kLaneThreads), kLaneThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in16, out8);
         } else {
             compress_quality_kernel<G, T><<<grid, kThreads, 0, st>>>(xt, numel, ngroups, q, s, zp, in_aligned, out_aligned);
         }
@@ -1084,16 +1086,12 @@ cudaError_t launch_typed(Coder coder, const void* x, int64_t numel, int64_t ngro
         if constexpr (G <= 64) {
             const bool in16 = reinterpret_cast<uintptr_t>(x) % 16 == 0 && (G * sizeof(T)) % 16 == 0;
             const bool out8 = reinterpret_cast<uintptr_t>(q) % 8 == 0;
-            const int64_t blocks = (ngroups + kThreads - 1) / kThreads;
-            const int lane_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
-            compress_sym_lane_kernel<G, T><<<lane_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in16, out8);
+            compress_sym_lane_kernel<G, T><<<blocks_for(kLaneThreads), kLaneThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in16, out8);
         } else {
             static_assert(G == 128, "the two-lanes-per-group kernel is written for G = 128");
             const bool in8 = reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T)) == 0;
             const bool out4 = reinterpret_cast<uintptr_t>(q) % 4 == 0;
-            const int64_t blocks = (ngroups + kThreads / 2 - 1) / (kThreads / 2);
-            const int pair_grid = int(blocks < int64_t(grid) ? blocks : int64_t(grid));
-            compress_sym_pair_kernel<T><<<pair_grid, kThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in8, out4);
+            compress_sym_pair_kernel<T><<<blocks_for(kLaneThreads / 2), kLaneThreads, 0, st>>>(xt, numel, ngroups, *tab, q, s, in8, out4);
         }
         break;
     }
