@@ -173,14 +173,47 @@ __device__ __forceinline__ void store_codes(uint8_t* __restrict__ q, int64_t num
 
 // ------------------------------------------------------------------ quality mode
 
+// min(a^2, b^2, c^2) as the square of the smallest magnitude: rounding a square is monotone in the magnitude, so the
+// result is the same number with one multiplication instead of three (the arguments are finite here).
+__device__ __forceinline__ float min_square(float a, float b, float c) {
+    const float m = fminf(fminf(fabsf(a), fabsf(b)), fabsf(c));
+    return __fmul_rn(m, m);
+}
+
+// What the three code trials of the quality mode need from a candidate.  The decoded value of code c (before its bf16
+// rounding) is (c - zp) * s with c - zp an integer of at most 9 bits and s a bf16 value (8 bits): exact in fp32, and so are
+// its neighbours' as that value -+ s.  s > 0, so clamping the CODE to [0, 255] and clamping the VALUE to
+// [(0 - zp) s, (255 - zp) s] select the same number: t = (r - zp) s, then clamp(t), clamp(t - s), clamp(t + s) replace three
+// clamps, two additions, three subtractions and three products by one of each of the latter two, two additions and
+// three clamps.  (|r| stays below 600 for the candidates of the search, so t is exact; were it not, it would lie outside
+// the range on the side it belongs to and clamp to the same bound.)
+struct QualityCand {
+    float s, zp, lo, hi;
+    __device__ __forceinline__ float clampv(float v) const { return fminf(fmaxf(v, lo), hi); }
+    __device__ __forceinline__ void trials(float r, float& v0, float& vm, float& vp) const {
+        const float t = __fmul_rn(__fsub_rn(r, zp), s);
+        v0 = clampv(t);
+        vm = clampv(__fsub_rn(t, s));
+        vp = clampv(__fadd_rn(t, s));
+    }
+};
+
+__device__ __forceinline__ QualityCand make_quality_cand(float s, float zp) {
+    QualityCand c;
+    c.s = s;
+    c.zp = zp;
+    c.lo = __fmul_rn(__fsub_rn(0.0f, zp), s);
+    c.hi = __fmul_rn(__fsub_rn(255.0f, zp), s);
+    return c;
+}
+
 // The smallest decoded squared error over the codes r - 1, r, r + 1 (each clamped): what the candidate search of the
 // quality mode scores.  The values are finite here (NaN / Inf were cleaned), so a plain minimum equals the reference's
 // NaN-propagating one.
-__device__ __forceinline__ float quality_error(float x, float s, float zp, float r) {
-    const float d0 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(r), zp), s)));
-    const float d1 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r, -1.0f)), zp), s)));
-    const float d2 = __fsub_rn(x, round_bf16(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r, 1.0f)), zp), s)));
-    return fminf(fminf(__fmul_rn(d0, d0), __fmul_rn(d1, d1)), __fmul_rn(d2, d2));
+__device__ __forceinline__ float quality_error(float x, const QualityCand& cand, float r) {
+    float v0, vm, vp;
+    cand.trials(r, v0, vm, vp);
+    return min_square(__fsub_rn(x, round_bf16(v0)), __fsub_rn(x, round_bf16(vm)), __fsub_rn(x, round_bf16(vp)));
 }
 
 // quality_error for two values at once: the six bf16 roundings become three packed conversions (the capture of
@@ -191,17 +224,17 @@ __device__ __forceinline__ void round_bf16_pair(float a, float b, float& ra, flo
     ra = __uint_as_float(w << 16);
     rb = __uint_as_float(w & 0xffff0000u);
 }
-__device__ __forceinline__ void quality_error2(float x0, float x1, float s, float zp, float r0, float r1, float& e0, float& e1) {
-    float a0, a1, b0, b1, c0, c1;
-    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(r0), zp), s), __fmul_rn(__fsub_rn(clamp255(r1), zp), s), a0, a1);
-    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r0, -1.0f)), zp), s),
-                    __fmul_rn(__fsub_rn(clamp255(__fadd_rn(r1, -1.0f)), zp), s), b0, b1);
-    round_bf16_pair(__fmul_rn(__fsub_rn(clamp255(__fadd_rn(r0, 1.0f)), zp), s),
-                    __fmul_rn(__fsub_rn(clamp255(__fadd_rn(r1, 1.0f)), zp), s), c0, c1);
+__device__ __forceinline__ void quality_error2(float x0, float x1, const QualityCand& cand, float r0, float r1, float& e0, float& e1) {
+    float a0, a1, b0, b1, c0, c1, v0, vm0, vp0, v1, vm1, vp1;
+    cand.trials(r0, v0, vm0, vp0);
+    cand.trials(r1, v1, vm1, vp1);
+    round_bf16_pair(v0, v1, a0, a1);
+    round_bf16_pair(vm0, vm1, b0, b1);
+    round_bf16_pair(vp0, vp1, c0, c1);
     const float da0 = __fsub_rn(x0, a0), db0 = __fsub_rn(x0, b0), dc0 = __fsub_rn(x0, c0);
     const float da1 = __fsub_rn(x1, a1), db1 = __fsub_rn(x1, b1), dc1 = __fsub_rn(x1, c1);
-    e0 = fminf(fminf(__fmul_rn(da0, da0), __fmul_rn(db0, db0)), __fmul_rn(dc0, dc0));
-    e1 = fminf(fminf(__fmul_rn(da1, da1), __fmul_rn(db1, db1)), __fmul_rn(dc1, dc1));
+    e0 = min_square(da0, db0, dc0);
+    e1 = min_square(da1, db1, dc1);
 }
 
 // code choice of the reference's _amo_quality_codes for one value whose rounded index r = rint(x / s + zp)
@@ -273,11 +306,12 @@ compress_quality_kernel(const T* __restrict__ x, int64_t numel, int64_t ngroups,
             const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
             const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
             const float rcp = __frcp_rn(s);
+            const QualityCand cand = make_quality_cand(s, zp);
             // rounded index from the exact quotient (the scale is a bf16 value), then the three-way code choice
             float e[VPL];
 #pragma unroll
             for (int i = 0; i < VPL; i += 2)
-                quality_error2(v[i], v[i + 1], s, zp, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)),
+                quality_error2(v[i], v[i + 1], cand, rintf(__fadd_rn(exact_quotient(v[i], s, rcp), zp)),
                                rintf(__fadd_rn(exact_quotient(v[i + 1], s, rcp), zp)), e[i], e[i + 1]);
             if (finmask != kAllFinite) {  // rare: positions that held NaN / Inf do not count
 #pragma unroll
@@ -661,12 +695,13 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
             const float s = __uint_as_float(uint32_t(use & 0xffff) << 16);
             const float zp = clamp255(rintf(__fdiv_rn(nlower, s)));
             const float rcp = __frcp_rn(s);
+            const QualityCand cand = make_quality_cand(s, zp);
             LaneSums<G> sums;
             if (finmask == kAllFinite) {
 #pragma unroll
                 for (int k = 0; k < G; k += 2) {
                     float e0, e1;
-                    quality_error2(v[k], v[k + 1], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)),
+                    quality_error2(v[k], v[k + 1], cand, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)),
                                    rintf(__fadd_rn(exact_quotient(v[k + 1], s, rcp), zp)), e0, e1);
                     sums.add(k, e0);
                     sums.add(k + 1, e1);
@@ -674,7 +709,7 @@ compress_quality_lane_kernel(const T* __restrict__ x, int64_t numel, int64_t ngr
             } else {
 #pragma unroll
                 for (int k = 0; k < G; ++k) {
-                    const float e = quality_error(v[k], s, zp, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
+                    const float e = quality_error(v[k], cand, rintf(__fadd_rn(exact_quotient(v[k], s, rcp), zp)));
                     sums.add(k, ((finmask >> k) & 1u) ? e : 0.0f);
                 }
             }
