@@ -432,7 +432,7 @@ def student_t_tensor(device, gen, B, R, C):
 
 # thread instructions per value the encoders execute, from the ncu captures under profiles/ (issue-slot bound of the ALU work)
 ENCODER_INSTR_PER_VALUE = {"fast": 14.3 * 16 + 10, "balanced": 14.3 * 32 + 10, "accurate": 14.3 * 48 + 10, "max": 14.3 * 64 + 10,
-                           "quality": 1700.0}
+                           "quality": 1629.0}
 
 
 def alu_estimate(mode: str, sm_mhz: float, sms: int = 148):
