@@ -179,7 +179,7 @@ TCB_API int tcb_decompress_sym(const int8_t* q, const uint16_t* scales, uint16_t
  *   quant_is_rhs != 0:  out = dense . deq(q)^T   (quantised weight; bias has R_q entries)
  *   quant_is_rhs == 0:  out[R_q, R_d] = deq(q) . dense^T  (the reference's layout: quantised
  *                       activation, dense weight; bias has R_d entries)
- * Requirements: G in {16, 32, 64}, K a positive multiple of G (the kernel steps K by
+ * Requirements: G in {16, 32, 64, 128}, K a positive multiple of G (the kernel steps K by
  * 64 and zero-fills a ragged last step); dense and q 16-byte aligned.  R_d and R_q
  * are arbitrary (edge tiles are masked).
  * Every wait inside the kernel is bounded; if one runs out the kernel records it

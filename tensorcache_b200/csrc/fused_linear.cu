@@ -519,7 +519,8 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
         const int pw = warp - kFirstProducerWarp;              // 0..7: rows [16 pw, 16 pw + 16) of the CTA's tile
         constexpr int kLog2Ts = LOG2_G - 1;                    // stages per table = 32 * G / 64
         constexpr int kTsMask = (1 << kLog2Ts) - 1;
-        constexpr int kGroupsPerStage = 64 >> LOG2_G;          // 4, 2, 1
+        constexpr int kGroupsPerStage = LOG2_G <= 6 ? (64 >> LOG2_G) : 1;   // 4, 2, 1; G = 128: one group per TWO stages
+        constexpr int kStagesPerGroupLog2 = LOG2_G <= 6 ? 0 : LOG2_G - 6;
         const int tables_per_tile = (num_kb + kTsMask) >> kLog2Ts;
         // conversion role of this lane: 16 codes at quarter kq of rows ra and ra + 8
         const int ra = pw * 16 + (lane >> 2), kq = lane & 3;
@@ -562,8 +563,9 @@ fused_dequant_gemm_kernel(const __grid_constant__ CUtensorMap dense_map, const _
                     fetch_next_table();
                     __syncwarp();
                 }
-                const uint32_t sz_a = *reinterpret_cast<const uint32_t*>(t_lane + j * (kGroupsPerStage * 4));
-                const uint32_t sz_b = *reinterpret_cast<const uint32_t*>(t_lane + 8 * kTableRowBytes + j * (kGroupsPerStage * 4));
+                const int t_word = (j >> kStagesPerGroupLog2) * (kGroupsPerStage * 4);   // byte offset of the stage's first group
+                const uint32_t sz_a = *reinterpret_cast<const uint32_t*>(t_lane + t_word);
+                const uint32_t sz_b = *reinterpret_cast<const uint32_t*>(t_lane + 8 * kTableRowBytes + t_word);
                 // the verdict of the wait is made warp-uniform: the warp-level syncs below need every lane
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(FULL_C + s), ph, abort_flag, abort_peer, (3 << 8) | (FULL_C + s)));
                 if (!ok) break;
@@ -714,7 +716,8 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
                                         int group_size, int quant_is_rhs, void* stream) {
     const char* who = "tcb_fused_dequant_linear";
     if (R_d < 0 || R_q < 0 || K < 0) return tcb::fail(TCB_ERR_BAD_ARG, "%s: negative size", who);
-    if (!tcb::core_group_size_ok(group_size)) return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64}", who, group_size);
+    if (!tcb::core_group_size_ok(group_size) && group_size != 128)
+        return tcb::fail(TCB_ERR_GROUP_SIZE, "%s: group_size %d not in {16, 32, 64, 128}", who, group_size);
     if (R_d == 0 || R_q == 0) return TCB_OK;
     if (K <= 0 || K % group_size != 0)
         return tcb::fail(TCB_ERR_BAD_ARG, "%s: K = %lld must be a positive multiple of the group size %d", who, (long long)K, group_size);
@@ -758,14 +761,15 @@ extern "C" int tcb_fused_dequant_linear(const uint16_t* dense, const uint8_t* q,
 
     // one instantiation per (group size, zero points or not): those are compile-time in the producer warps
     typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Params);
-    static const KernelFn kernels[3][2] = {
+    static const KernelFn kernels[4][2] = {
         {fused_dequant_gemm_kernel<4, false>, fused_dequant_gemm_kernel<4, true>},
         {fused_dequant_gemm_kernel<5, false>, fused_dequant_gemm_kernel<5, true>},
-        {fused_dequant_gemm_kernel<6, false>, fused_dequant_gemm_kernel<6, true>}};
-    const int gi = group_size == 16 ? 0 : group_size == 32 ? 1 : 2;
+        {fused_dequant_gemm_kernel<6, false>, fused_dequant_gemm_kernel<6, true>},
+        {fused_dequant_gemm_kernel<7, false>, fused_dequant_gemm_kernel<7, true>}};
+    const int gi = group_size == 16 ? 0 : group_size == 32 ? 1 : group_size == 64 ? 2 : 3;
     const int zi = zp_or_null ? 1 : 0;
     const KernelFn kernel = kernels[gi][zi];
-    static std::atomic<bool> attr_set[64][3][2] = {};
+    static std::atomic<bool> attr_set[64][4][2] = {};
     int dev = 0;
     TCB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev][gi][zi].load(std::memory_order_acquire)) {

@@ -24,7 +24,7 @@ import torch.nn as nn
 
 from . import _lib
 
-SUPPORTED_GROUP_SIZES = (16, 32, 64)  # group sizes the tensor-core kernel is instantiated for
+SUPPORTED_GROUP_SIZES = (16, 32, 64, 128)  # group sizes the tensor-core kernel is instantiated for
 
 
 def _ptr(t: Optional[torch.Tensor]):

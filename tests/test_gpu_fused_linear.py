@@ -31,7 +31,7 @@ def rel_fro(got, ref):
 
 
 @pytest.mark.parametrize("M,N,K,G", [(256, 128, 64, 32), (128, 512, 768, 32), (300, 200, 256, 16), (77, 1000, 1024, 64),
-                                     (1, 1, 64, 32), (2048, 1536, 2048, 32),
+                                     (1, 1, 64, 32), (2048, 1536, 2048, 32), (300, 520, 1024, 128), (64, 64, 128, 128), (512, 256, 4352, 128),
                                      # inner dimensions that are not a multiple of the kernel's K step of 64
                                      (200, 300, 96, 32), (130, 70, 80, 16), (256, 384, 4000, 32), (64, 64, 192, 64), (33, 77, 16, 16)])
 @pytest.mark.parametrize("with_bias", [False, True])
