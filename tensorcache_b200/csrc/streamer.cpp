@@ -259,10 +259,11 @@ gather_host_rows_kernel(const GatherBatch g) {
     const GatherSegment sg = g.seg[k];
     const int64_t total = sg.units_per_row * g.n_rows;
     const int64_t stride = int64_t(sg.blocks) * blockDim.x;
-    for (int64_t u0 = int64_t(int(blockIdx.x) - sg.first_block) * blockDim.x + threadIdx.x; u0 < total; u0 += 4 * stride) {
-        uint4 v[4];
+    constexpr int kInFlight = 8;   // 16-byte loads per thread before the first store (4: 2-5 % less on the same link)
+    for (int64_t u0 = int64_t(int(blockIdx.x) - sg.first_block) * blockDim.x + threadIdx.x; u0 < total; u0 += kInFlight * stride) {
+        uint4 v[kInFlight];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kInFlight; ++i) {
             const int64_t u = u0 + i * stride;
             if (u < total) {
                 const int64_t r = u / sg.units_per_row;
@@ -270,7 +271,7 @@ gather_host_rows_kernel(const GatherBatch g) {
             }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kInFlight; ++i) {
             const int64_t u = u0 + i * stride;
             if (u < total) sg.dst[u] = v[i];
         }
