@@ -247,6 +247,38 @@ def cpu_torch_baseline(numel: int, g: int):
                       f"tensors with out_buffer, torch.get_num_threads() = {torch.get_num_threads()}"}
 
 
+def cpu_reference_streamer(prefix: str, first_batch_bits, max_batches: int = 32):
+    """The reference's OWN reader on the host: the unmodified ZeroCopyTensorStreamer(device="cpu") (src/tensorcache/streamer.py:334-372)
+    over shard 0 of the cache THIS build's writer produced, contiguous order.  Also an interoperability check: its first
+    batch must carry the bits this build's reader delivered for the same rows."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "tensorcache").is_dir():
+        return {"unavailable": "baseline/_ref/tensorcache is absent (python baseline/install_ref.py puts the reference package there)"}
+    sys.path.insert(0, str(ref_dir))
+    try:
+        from tensorcache.streamer import ZeroCopyTensorStreamer as RefStreamer
+    except Exception as e:   # noqa: BLE001
+        return {"unavailable": f"the reference package does not import here: {e}"}
+    finally:
+        sys.path.remove(str(ref_dir))
+    try:
+        st = RefStreamer(prefix, batch_size=SHAPE[0], device="cpu", shuffle=False, shard_idx=0)
+        n, same, t0 = 0, None, time.perf_counter()
+        for k, batch in enumerate(st):
+            if k == 0 and first_batch_bits is not None:
+                same = bool(torch.equal(batch.view(torch.int16), first_batch_bits))
+            n += int(batch.shape[0])
+            if k + 1 >= max_batches:
+                break
+        spent = time.perf_counter() - t0
+        st.close()
+    except Exception as e:   # noqa: BLE001
+        return {"unavailable": f"the reference reader failed on this cache: {type(e).__name__}: {e}"}
+    return {"samples_per_s": n / spent, "batches": max_batches, "cores": torch.get_num_threads(),
+            "first_batch_bit_equal_with_this_build": same,
+            "note": "unmodified reference ZeroCopyTensorStreamer(device='cpu', shuffle=False, shard_idx=0) over the cache written here"}
+
+
 def run_reference_arm(args):
     """CPU port of the reference decode, all host threads; step = one decode of the full workload."""
     rank = int(os.environ.get("RANK", "0"))
@@ -848,6 +880,11 @@ def main():
             t_pin = time.perf_counter() - t_pin
             default_mode = "resident (shards page-locked)" if st.pin_shard else "staging copies"
             samples_per_rank = st.num_samples
+            first_bits = None
+            if rank == 0 and not args.no_extras:
+                for b in st:     # the first batch of shard 0, kept for the comparison with the reference's own reader
+                    first_bits = b.view(torch.int16).cpu()
+                    break
             times["default_contig"], d2h = time_batches(lambda: iter(st), device, e2e_steps, args.warmup, barrier)
             st.shuffle = True
             times["default_random"], _ = time_batches(lambda: iter(st), device, e2e_steps, args.warmup, barrier)
@@ -862,6 +899,7 @@ def main():
                 lambda: ds.iter_batches(batch_size=SHAPE[0], shuffle=False, device=str(device)), device, e2e_steps, args.warmup, barrier)
             iter_mode = "resident (shards page-locked)" if ds.pin_shard else "staging copies"
             ds.close()
+            ref_reader = cpu_reference_streamer(prefix, first_bits) if (rank == 0 and not args.no_extras) else None
         finally:
             barrier()
             if rank == 0:
@@ -894,7 +932,7 @@ def main():
                        "decode -> D2H completion word, every batch; the clock starts before a fresh pass begins"}
         streamer = {"samples_per_s": rate, "bf16_equiv_gbs_default_contig": rate["default_contig"] * SHAPE[1] * SHAPE[2] * 2 / 1e9,
                     "default_mode": default_mode, "iter_batches_mode": iter_mode, "open_seconds_default_mode": t_pin,
-                    "writer_samples_per_s_per_rank": writer_rate_min,
+                    "writer_samples_per_s_per_rank": writer_rate_min, "reference_cpu_streamer": ref_reader,
                     "samples_per_rank": samples_per_rank, "batch_size": SHAPE[0], "batches_timed": e2e_steps,
                     "note": "default_* = pin_shard=None (what a drop-in user gets); staging_* = pin_shard=False (rows copied into "
                             "page-locked staging by worker threads, the reference's scheme); iter_batches = FeatureCacheDataset.iter_batches"}
