@@ -475,6 +475,32 @@ def alu_estimate(mode: str, sm_mhz: float, sms: int = 148):
     return sms * 4 * 32 * sm_mhz * 1e6 / per_value / 1e9
 
 
+def reference_cpu_compress_c0(tc, device):
+    """The reference's OWN CPU encoder (unmodified package under baseline/_ref, src/tensorcache/codec.py:774-893) on the
+    correctness configuration, a bf16 [16,446,768] batch of the seed-0 feature stream, balanced G32; and whether this build's
+    GPU encoder returns the same codes, scale bits and zero points for it."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "tensorcache").is_dir():
+        return {"unavailable": "baseline/_ref/tensorcache is absent"}
+    sys.path.insert(0, str(ref_dir))
+    try:
+        import tensorcache as ref
+    except Exception as e:   # noqa: BLE001
+        return {"unavailable": f"the reference package does not import here: {e}"}
+    finally:
+        sys.path.remove(str(ref_dir))
+    x = feature_slice(device, 0, 0, 16)
+    xc = x.cpu()
+    t0 = time.perf_counter()
+    q, s, zp, _ = ref.compress(xc, mode="balanced", group_size=G)
+    spent = time.perf_counter() - t0
+    q2, s2, zp2, _ = tc.compress(x, "balanced", G)
+    same = bool(torch.equal(q.view(-1), q2.cpu().view(-1)) and torch.equal(s.view(torch.int16).view(-1), s2.cpu().view(torch.int16).view(-1))
+                and torch.equal(zp.view(-1), zp2.cpu().view(-1)))
+    return {"gvalues_per_s": xc.numel() / spent / 1e9, "ms": spent * 1e3, "cores": torch.get_num_threads(),
+            "bit_equal_with_this_build": same, "note": "one run of the reference's compress() on CPU tensors, bf16 [16,446,768]"}
+
+
 def kernels_section(tc, device, gpu_index):
     """Throughput of the encoder (bf16 [256,1024,1024], three modes x G16 / G32) and of the fused dequantise + GEMM
     (X [8192,4096] x AMO-BQ W [14336,4096]) with the SM clock sampled over each region."""
@@ -500,6 +526,7 @@ def kernels_section(tc, device, gpu_index):
                     "gvalues_per_s_if_every_issue_slot_were_busy": est, "frac": gv / est,
                     "thread_instructions_per_value": ENCODER_INSTR_PER_VALUE[mode]},
                 "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
+    out["compress"]["reference_cpu_c0_balanced_g32"] = reference_cpu_compress_c0(tc, device)
     out["compress"]["note"] = ("bf16 [256,1024,1024] Student-t(4) x lognormal(0,1) per channel; the encoders are ALU-bound (an exact division "
                                "and ~14 thread instructions per value and candidate), so the HBM fraction is low by construction")
     del x
@@ -522,6 +549,22 @@ def kernels_section(tc, device, gpu_index):
         tf = 2.0 * M * N * K / sec / 1e12
         fl[label] = {"tflops": tf, "ms": sec * 1e3, "launches": steps, "frac_of_burst": tf / burst, "frac_of_sustained": tf / sustained,
                      "sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
+    # The accuracy oracle's expression at full size on the host: fp32 dequantise-then-matmul on CPU tensors (one run), and
+    # the relative Frobenius error of the kernel's bf16 result against it.
+    try:
+        y = tc.fused_dequant_matmul(xx, wq, ws, wzp, None, G)
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        w32 = ((wq.cpu().float().view(N, K // G, G) - wzp.cpu().float().view(N, K // G, 1)) * ws.cpu().float().view(N, K // G, 1)).view(N, K)
+        ref = xx.cpu().float() @ w32.T
+        spent = time.perf_counter() - t0
+        yc = y.cpu().float()
+        fl["reference_cpu_fp32"] = {"tflops": 2.0 * M * N * K / spent / 1e12, "ms": spent * 1e3, "cores": torch.get_num_threads(),
+                                    "rel_frobenius_error_of_the_kernel": float((yc - ref).norm() / ref.norm()),
+                                    "note": "fp32 dequantise-then-matmul of the same operands by torch on the host (one run, dequantisation included)"}
+        del y, w32, ref, yc
+    except Exception as e:   # noqa: BLE001  (host memory: the leg needs about 1.5 GB)
+        fl["reference_cpu_fp32"] = {"unavailable": f"{type(e).__name__}: {e}"}
     fl["workload"] = f"X[{M},{K}] bf16 (N(0,1)) x AMO-BQ balanced G32 W[{N},{K}] (N(0, std 0.02)) -> bf16 [{M},{N}]"
     fl["peaks"] = {"bf16_tflops_burst": burst, "bf16_tflops_sustained": sustained, "kind": kind}
     fl["note"] = ("'burst' is 20 launches timed alone (compare with the burst peak), 'long' 1500 launches during which the GPU settles under "
