@@ -261,6 +261,11 @@ def cpu_reference_streamer(prefix: str, first_batch_bits, max_batches: int = 32)
         return {"unavailable": f"the reference package does not import here: {e}"}
     finally:
         sys.path.remove(str(ref_dir))
+    # under torchrun OMP_NUM_THREADS is 1; give the reference this rank's share of the host cores for the leg
+    had = torch.get_num_threads()
+    share = max(1, (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+                // max(1, int(os.environ.get("LOCAL_WORLD_SIZE") or os.environ.get("WORLD_SIZE") or 1)))
+    torch.set_num_threads(max(had, share))
     try:
         st = RefStreamer(prefix, batch_size=SHAPE[0], device="cpu", shuffle=False, shard_idx=0)
         n, same, t0 = 0, None, time.perf_counter()
@@ -273,8 +278,11 @@ def cpu_reference_streamer(prefix: str, first_batch_bits, max_batches: int = 32)
         spent = time.perf_counter() - t0
         st.close()
     except Exception as e:   # noqa: BLE001
+        torch.set_num_threads(had)
         return {"unavailable": f"the reference reader failed on this cache: {type(e).__name__}: {e}"}
-    return {"samples_per_s": n / spent, "batches": max_batches, "cores": torch.get_num_threads(),
+    used = torch.get_num_threads()
+    torch.set_num_threads(had)
+    return {"samples_per_s": n / spent, "batches": max_batches, "cores": used,
             "first_batch_bit_equal_with_this_build": same,
             "note": "unmodified reference ZeroCopyTensorStreamer(device='cpu', shuffle=False, shard_idx=0) over the cache written here"}
 
