@@ -86,6 +86,25 @@ def test_module_with_amo_activation_codes():
     assert rel_fro(y, ref) <= EXPECTED
 
 
+@pytest.mark.parametrize("G", [64, 128])
+def test_module_with_wide_groups_and_identity_bits(G):
+    """The layer form with G = 64 / 128 (at 128 one scale spans two of the kernel's K steps), and the identity check at
+    those group sizes: the dequantised operand is bit-identical with tc.decompress."""
+    M, K, N = 300, 1024, 260
+    layer = tc.FusedDequantLinear(K, N, bias=True, group_size=G).to(DEV)
+    a = synth.config0_style(10 + G, (M, K)).to(DEV)
+    q, s, zp, _ = tc.compress(a, "balanced", G)
+    y = layer(q.view(M, K), s, zp)
+    check_device_status()
+    ref = dequant_f32(q.view(M, K), s, zp, G) @ layer.weight.float().T + layer.bias.float()
+    assert rel_fro(y, ref) <= EXPECTED
+    eye = torch.eye(K, dtype=torch.bfloat16, device=DEV)
+    back = tc.fused_dequant_matmul(eye, q.view(M, K), s, zp, None, G)      # [K, M] = deq(A)^T
+    check_device_status()
+    want = tc.decompress(q, s, (M, K), zp, G)
+    assert torch.equal(back.t().contiguous().view(torch.int16), want.view(torch.int16))
+
+
 def test_dequantised_operand_equals_the_decode_kernel_bits():
     """With an identity dense operand the GEMM returns the dequantised operand itself:
     it must be bit-identical with tc.decompress (same arithmetic, exact accumulation)."""
