@@ -519,7 +519,7 @@ def kernels_section(tc, device, gpu_index):
     x = student_t_tensor(device, gen, 256, 1024, 1024)
     hbm, _ = peaks()
     for mode in ("fast", "balanced", "quality"):
-        for g in (16, 32):
+        for g in ((16, 32, 128) if mode == "balanced" else (16, 32)):   # G128: the two-lanes-per-group kernel
             steps = 8 if mode == "quality" else 30
             sampler = ClockSampler(gpu_index)
             sampler.start()
