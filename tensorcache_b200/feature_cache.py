@@ -52,12 +52,12 @@ class FeatureCacheWriter:
         self._resolve_settings(output_prefix, num_samples, seq_len, dim, group_size, adaptive, amo_bq, amo_lo, amo_hi,
                                amo_candidates, amo_mode, num_shards, quant_bits, resume)
         self._open_maps(resume)
-        self._start_prefault(prefault, resume)
-
-    def _start_prefault(self, wanted: Optional[bool], resume: bool) -> None:
         self._prefaulter = None
-        if wanted is False or resume:      # an appended-to cache already has most of its pages
-            return
+        self._prefault_plan = None if (prefault is False or resume) else (prefault,)   # started by the first append()
+
+    def _start_prefault(self, wanted: Optional[bool]) -> None:
+        """Runs on the first append (a writer that never receives data allocates nothing).  Caches reopened for appending are
+        left alone: they already have most of their pages."""
         spans = [(int(mm.ctypes.data), int(mm.nbytes)) for maps in self._maps if maps is not None for mm in maps]
         total = sum(n for _, n in spans)
         if wanted is None:
@@ -285,6 +285,9 @@ class FeatureCacheWriter:
             raise ValueError(f"expected [..., {self.seq_len}, {self.dim}], got {tuple(tensor_bf16.shape)}")
         if self.current_idx + B > self.num_samples:
             raise ValueError(f"Exceeds pre-allocated {self.num_samples}: have {self.current_idx}, adding {B}")
+        if getattr(self, "_prefault_plan", None) is not None:
+            plan, self._prefault_plan = self._prefault_plan, None
+            self._start_prefault(plan[0])
         done, k, pending = 0, 0, None
         while done < B:
             cur = min(self._CHUNK, B - done)

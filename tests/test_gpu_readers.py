@@ -338,8 +338,10 @@ def test_background_page_population_changes_no_byte(tmp_path, prefault):
         assert plain._prefaulter is None
         plain.append(x.to(DEV)); plain.close()
         w = tc.FeatureCacheWriter(root / "feat", 400, 16, 128, prefault=prefault, **kw)
+        assert w._prefaulter is None                                  # nothing is populated before data arrives
+        w.append(x[:100].to(DEV))
         assert (w._prefaulter is not None) == (prefault is True or root == shm)
-        w.append(x[:100].to(DEV)); w.append(x[100:]); w.close()      # 300 of 400 samples: the last shard stays partly empty
+        w.append(x[100:]); w.close()                                  # 300 of 400 samples: the last shard stays partly empty
         assert w._prefaulter is None
         for f in sorted((tmp_path / "a").iterdir()):
             if f.suffix == ".bin":
