@@ -1028,7 +1028,7 @@ def main():
             "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u8->bf16 (fp32 arithmetic)", "data": "synthetic",
             "config": workload_config(world),
-            "timing": {"launch": "eager" if args.no_graph else f"CUDA graphs of {GRAPH_LAUNCHES} launches",
+            "timing": {"launch": "eager" if args.no_graph else f"CUDA graphs of {min(GRAPH_LAUNCHES, args.steps)} launches",
                        "untimed_launches_enqueued_directly_before_the_start_event": pre_roll,
                        "l2_policy": f"{n_sets} rotating input/output sets ({n_sets * bytes_per_step / 1e6:.0f} MB) > 126 MB L2",
                        "cache": None if c4 is None else f"one {c4['samples']}-sample cache of {C4_SHARDS} shards "
